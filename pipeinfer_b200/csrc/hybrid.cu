@@ -27,7 +27,8 @@ struct pib_hybrid_ctx {
     int cap = 0;
     float * x = nullptr, * h = nullptr, * y = nullptr, * proj = nullptr, * cq = nullptr, * q = nullptr, * qlat = nullptr, * lat = nullptr, * att = nullptr;
     float * rlog = nullptr, * wts = nullptr, * eup = nullptr, * edn = nullptr, * ysh = nullptr;
-    float * h2 = nullptr, * cv = nullptr, * vfirst = nullptr, * mixes = nullptr;   // parallel layers: second norm; convolved q | k | v; first mixing layer's values; token-shift mixes
+    float * h2 = nullptr, * cv = nullptr, * vfirst = nullptr, * mixes = nullptr;   // parallel layers: second norm (pre-norm layers: the stream's second buffer); convolved q | k | v; first mixing layer's values; token-shift mixes
+    float * cat = nullptr;                      // [stream ; embedding] rows of models whose layers are walked again
     int32_t * ids = nullptr, * perm = nullptr, * inv = nullptr, * counts = nullptr, * offs = nullptr;
     // batch bookkeeping: pinned staging ring + device copy
     static const int RING = 4;
@@ -49,11 +50,14 @@ static const char * const HK_NAMES[] = { "cellmap", "embed_ln", "canon_conv", "m
                                          "mm_qfv", "hgrn2_gates", "hgrn2_scan", "mm_hgrn2_o", "ln_residual", "mm_up", "polynorm", "mm_down", "mm_router", "moe_route",
                                          "moe_sort", "mm_experts_up", "mm_experts_down", "mm_shared_up", "mm_shared_down", "moe_combine", "final_ln", "mm_head", "sample", "latent_attention_mm",
                                          "embed_scale", "rms_norm_pair", "mm_qkv", "qkv_conv", "attn_prep", "kv_attention", "kv_attention_mm", "token_shift", "mm_rkvg", "mm_decay",
-                                         "decay_act", "wkv_scan", "delta_prep", "delta_scan", "gated_head_norm", "glu_clamp", "parallel_sum" };
+                                         "decay_act", "wkv_scan", "delta_prep", "delta_scan", "gated_head_norm", "glu_clamp", "parallel_sum",
+                                         "embed_pair", "prenorm_shift", "loop_concat", "mm_loop_in", "mm_ssm_in", "ssm_conv", "mm_ssm_x", "mm_ssm_dt", "ssm_scan", "mm_ssm_o",
+                                         "mm_dual_proj", "dual_prep", "decay_scan", "dual_gate", "mm_dual_o", "xielu" };
 enum { HK_CELLMAP, HK_EMBED, HK_CANON, HK_DQKV, HK_LPREP, HK_UQ, HK_ABSORB, HK_LATTN, HK_UV, HK_AO, HK_QFV, HK_GATES, HK_SCAN, HK_HO, HK_LNRES, HK_UP, HK_POLY, HK_DOWN,
        HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_LATTN_MM,
        HK_EMBSCALE, HK_NORM2, HK_QKV, HK_QKVCONV, HK_APREP, HK_KVATTN, HK_KVATTN_MM, HK_SHIFT, HK_RKVG, HK_DECAY, HK_DECAYACT, HK_WKVSCAN, HK_DPREP, HK_DSCAN, HK_GHNORM, HK_GLU,
-       HK_PSUM, HK_COUNT };
+       HK_PSUM, HK_EMBPAIR, HK_PRENORM, HK_CONCAT, HK_LOOPIN, HK_SSMIN, HK_SSMCONV, HK_SSMX, HK_SSMDT, HK_SSMSCAN, HK_SSMO, HK_DUALPROJ, HK_DUALPREP, HK_DECAYSCAN, HK_DUALGATE,
+       HK_DUALO, HK_XIELU, HK_COUNT };
 const char * pib_hybrid_kind_name(int k) { return k >= 0 && k < HK_COUNT ? HK_NAMES[k] : "?"; }
 
 // fetch and clear the records; returns the count (the stream is synchronised)
@@ -138,9 +142,9 @@ static int grow_attn_mm(pib_context * c, size_t kw, size_t kx, int q_rows, int s
 static void free_scratch(pib_hybrid_ctx * x) {
     for (void * b : { (void *) x->x, (void *) x->h, (void *) x->y, (void *) x->proj, (void *) x->cq, (void *) x->q, (void *) x->qlat, (void *) x->lat, (void *) x->att,
                       (void *) x->rlog, (void *) x->wts, (void *) x->eup, (void *) x->edn, (void *) x->ysh, (void *) x->ids, (void *) x->perm, (void *) x->inv,
-                      (void *) x->counts, (void *) x->offs, (void *) x->h2, (void *) x->cv, (void *) x->vfirst, (void *) x->mixes }) if (b) cudaFree(b);
+                      (void *) x->counts, (void *) x->offs, (void *) x->h2, (void *) x->cv, (void *) x->vfirst, (void *) x->mixes, (void *) x->cat }) if (b) cudaFree(b);
     x->x = x->h = x->y = x->proj = x->cq = x->q = x->qlat = x->lat = x->att = x->rlog = x->wts = x->eup = x->edn = x->ysh = nullptr;
-    x->h2 = x->cv = x->vfirst = x->mixes = nullptr;
+    x->h2 = x->cv = x->vfirst = x->mixes = x->cat = nullptr;
     x->ids = x->perm = x->inv = x->counts = x->offs = nullptr;
     x->cap = 0;
 }
@@ -181,8 +185,8 @@ static int grow_scratch(pib_context * c, int T) {
                     fl(&x->qlat, (size_t) hy->w_lat) && fl(&x->lat, (size_t) hy->w_lat) && fl(&x->att, (size_t) hy->w_att) && fl(&x->rlog, (size_t) hy->w_router) &&
                     fl(&x->wts, (size_t) hy->w_pairs) && fl(&x->eup, (size_t) hy->w_eup) && fl(&x->edn, (size_t) hy->w_pairs * W) && fl(&x->ysh, hy->w_pairs ? W : 0) &&
                     in(&x->ids, n * hy->w_pairs) && in(&x->perm, n * hy->w_pairs) && in(&x->inv, n * hy->w_pairs) && in(&x->counts, (size_t) hy->w_router + 1) &&
-                    in(&x->offs, (size_t) hy->w_router + 2) && fl(&x->h2, hy->form == PIB_FORM_PARALLEL ? W : 0) && fl(&x->cv, (size_t) hy->w_conv) &&
-                    fl(&x->vfirst, (size_t) hy->w_vfirst) && fl(&x->mixes, (size_t) hy->w_shift);
+                    in(&x->offs, (size_t) hy->w_router + 2) && fl(&x->h2, hy->form != PIB_FORM_POSTNORM ? W : 0) && fl(&x->cv, (size_t) hy->w_conv) &&
+                    fl(&x->vfirst, (size_t) hy->w_vfirst) && fl(&x->mixes, (size_t) hy->w_shift) && fl(&x->cat, (size_t) hy->w_cat);
     if (!ok) { cudaGetLastError(); free_scratch(x); pib_set_error("decode: out of memory for the work buffers of %d tokens", T); return PIB_ERR_NOMEM; }
     x->cap = (int) n;
     return PIB_OK;
@@ -222,7 +226,11 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
     auto wbytes = [](const pib_weight * w) { return (double) w->bytes; };
     auto mmfl = [&](const pib_weight * w) { return 2.0 * Td * (double) w->N * (double) w->K; };
     auto mmby = [&](const pib_weight * w) { return (double) w->bytes + 4.0 * Td * ((double) w->N + (double) w->K); };
-    auto key_pairs = [&](int window) { double n = 0; for (int i = 0; i < T; i++) n += std::min(B_pos_host[i] + 1, window); return n; };
+    auto key_pairs = [&](int window, int mask = PIB_MASK_WINDOW) {
+        double n = 0;
+        for (int i = 0; i < T; i++) n += mask == PIB_MASK_CHUNK ? B_pos_host[i] % window + 1 : std::min(B_pos_host[i] + 1, window);
+        return n;
+    };
     auto mm = [&](const pib_weight * w, const float * X, int ldx, float * Y, int ldy, int epi) {
         pib_mm a;
         a.W = w->base; a.wtype = w->type; a.ldw = w->K; a.X = X; a.ldx = ldx; a.Y = Y; a.ldy = ldy; a.M = T; a.N = (int) w->N; a.K = (int) w->K; a.epi = epi;
@@ -344,6 +352,59 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
         return PIB_OK;
     };
+    // the attention of cached key / value heads over `q`: per-token kernel, or the matmul form for long portions in served mode
+    auto kv_attend = [&](const pib_hlayer & L, float * cache, int row, float * out) -> int {
+        const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim;
+        const double keys = key_pairs(L.window, L.mask);
+        const bool mm_ok = !exact && D % 8 == 0 && D >= 16 && V >= 16 && attn_mm_enabled();
+        bool any_mm = false, any_simt = false;
+        for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
+        if (any_simt)
+            RC(HK_KVATTN, 2.0 * keys * H * (D + V), 4.0 * keys * G * (D + V) + 4.0 * Td * H * (D + V),
+               pib_kv_attention(x->q, L, B, cache, row, x->cellmap, (int) c->n_ctx, out, any_mm ? B.mmflag : nullptr, st));
+        for (const pib_hseg & g : segs) {
+            if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
+            const int nb = (g.len + MM_ATTN_BLOCK - 1) / MM_ATTN_BLOCK, per = (g.len + nb - 1) / nb;      // blocks of equal size: none is left with a handful of rows
+            for (int o = 0; o < g.len; o += per) {
+                const int nq = std::min(per, g.len - o), p0 = B_pos_host[g.start + o];
+                const int j0 = L.mask == PIB_MASK_CHUNK ? p0 - p0 % L.window : std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
+                if ((rc = grow_attn_mm(c, (size_t) G * std::max(D, V), (size_t) 3 * G * D + V, nq * H, nq * H, NK)) != PIB_OK) return rc;
+                RC(HK_KVATTN_MM, 2.0 * nq * H * (double) NK * (D + 2.0 * V), 2.0 * NK * G * (D + 2.0 * V) + 8.0 * nq * H * (D + V) + 8.0 * nq * H * (double) NK,
+                   pib_kv_attention_mm(x->q, L, B, cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK, x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p,
+                                       out, st));
+                nk += 5;
+            }
+        }
+        return PIB_OK;
+    };
+    // selective state-space scan: u | z in one matmul, convolution + bias + silu on u, [dt | B | C] from u, dt widened to the channels, the scan
+    // (softplus, decays, the skip D u and the gate silu(z) inside), output matmul
+    auto mixer_ssm = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int I = L.inner, N = L.n_state, R = L.dt_rank, ldx = (R + 2 * N + 3) & ~3;
+        RC(HK_SSMIN, mmfl(L.ssm_in), mmby(L.ssm_in), mm(L.ssm_in, hin, W, x->proj, 2 * I, PIB_EPI_NONE));
+        RC(HK_SSMCONV, 2.0 * Td * I * L.taps, 8.0 * Td * I, pib_chan_conv(x->proj, 2 * I, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, I, x->cv, I, 0, 1, st, L.conv_b));
+        nk += L.taps > 1;
+        RC(HK_SSMX, mmfl(L.ssm_x), mmby(L.ssm_x), mm(L.ssm_x, x->cv, I, x->cq, ldx, PIB_EPI_NONE));
+        RC(HK_SSMDT, mmfl(L.ssm_dt), mmby(L.ssm_dt), mm(L.ssm_dt, x->cq, ldx, x->lat, I, PIB_EPI_NONE));
+        RC(HK_SSMSCAN, 6.0 * Td * I * N, 4.0 * Td * (4.0 * I + 2.0 * N), pib_ssm_scan(x->cv, I, x->lat, I, x->cq + R, ldx, x->proj + I, 2 * I, L, B, x->state, hy->state_floats, x->att, st));
+        RC(HK_SSMO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, I, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
+    // two branches on the same input: every projection in one matmul; biases, rotation, unit norms, cache write and the linear branch's
+    // activations in one kernel; attention over the token's chunk; the constant-decay recurrence; gates, the norm over the linear branch's
+    // heads and both scales in one kernel; one output matmul over [softmax branch | linear branch] (its bias joins the residual sum)
+    auto mixer_dual = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, G = L.kv_heads, D = L.dim, H2 = L.heads2, D2 = L.dim2, V2 = L.vdim2, row = hy->cache_row[L.cache_id];
+        const int ldp = ((int) L.qkv->N + 3) & ~3, ga = (H + G) * D, q2 = ga + H, k2 = q2 + H2 * D2, v2 = k2 + H2 * D2, gb = v2 + H2 * V2;
+        float * cache = x->cache[L.cache_id];
+        RC(HK_DUALPROJ, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+        RC(HK_DUALPREP, 0, 8.0 * Td * ldp, pib_dual_prep(x->proj, ldp, L, eps, B, x->rope[L.rope_id], x->q, cache, row, st));
+        if ((rc = kv_attend(L, cache, row, x->lat)) != PIB_OK) return rc;
+        RC(HK_DECAYSCAN, 5.0 * Td * H2 * D2 * V2, 4.0 * Td * H2 * (2.0 * D2 + 2.0 * V2), pib_decay_scan(x->proj, ldp, q2, k2, v2, L, B, x->state, hy->state_floats, x->cv, st));
+        RC(HK_DUALGATE, 0, 8.0 * Td * (H * D + 2.0 * H2 * V2), pib_dual_gate(x->lat, x->cv, x->proj, ldp, ga, gb, L, eps, T, x->att, st));
+        RC(HK_DUALO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * D + H2 * V2, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
     auto run_mixer = [&](const pib_hlayer & L, const float * hin) -> int {
         switch (L.mixer) {
             case PIB_MIXER_LATENT: return mixer_latent(L, hin);
@@ -351,6 +412,8 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             case PIB_MIXER_SWA:    return mixer_swa(L, hin);
             case PIB_MIXER_WKV:    return mixer_wkv(L, hin);
             case PIB_MIXER_DELTA:  return mixer_delta(L, hin);
+            case PIB_MIXER_SSM:    return mixer_ssm(L, hin);
+            case PIB_MIXER_DUAL:   return mixer_dual(L, hin);
         }
         pib_set_error("decode: mixer %d", L.mixer);
         return PIB_ERR_UNSUPP;
@@ -389,12 +452,42 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
     };
 
     RC(HK_CELLMAP, 0, 16.0 * Td, pib_cellmap_set(x->cellmap, (int) c->n_ctx, B, st));
-    if (hy->form == PIB_FORM_PARALLEL) RC(HK_EMBSCALE, 0, 6.0 * Td * Wd, pib_embed_scale(m->tok_embd, B.tok, hy->embd_scale, T, W, x->x, st));
-    else                               RC(HK_EMBED, 0, 6.0 * Td * Wd, pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
+    if (hy->form == PIB_FORM_PARALLEL)     RC(HK_EMBSCALE, 0, 6.0 * Td * Wd, pib_embed_scale(m->tok_embd, B.tok, hy->embd_scale, T, W, x->x, st));
+    else if (hy->form == PIB_FORM_PRENORM) RC(HK_EMBPAIR, 0, (hy->loops ? 10.0 : 6.0) * Td * Wd, pib_embed_pair(m->tok_embd, B.tok, T, W, x->x, hy->loops ? x->cat : nullptr, st));
+    else                                   RC(HK_EMBED, 0, 6.0 * Td * Wd, pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
+    // pre-norm form: the stream is (have_x ? cur : 0) + pend_y + pend_b; the sum is formed by the next norm's kernel, which leaves it in the
+    // other of the two stream buffers (the block of the next token reads this token's inputs for the shift)
+    float * cur = x->x, * other = x->h2;
+    const float * pend_y = nullptr, * pend_b = nullptr;
+    bool have_x = true;
+    auto prenorm = [&](float g, const float * mu, size_t shift_off, bool keep) -> int {
+        const bool upd = keep && (pend_y || pend_b || !have_x);
+        RC(HK_PRENORM, 0, (upd ? 16.0 : 12.0) * Td * Wd, pib_prenorm_shift(have_x ? cur : nullptr, pend_y, pend_b, upd ? other : nullptr, g, eps, mu, B, x->state, hy->state_floats,
+                                                                         shift_off, W, x->h, st));
+        nk += mu != nullptr;
+        if (upd) { std::swap(cur, other); have_x = true; pend_y = pend_b = nullptr; }
+        return PIB_OK;
+    };
     for (int il = 0; il < m->n_layer; il++) {
         const pib_hlayer & L = hy->layers[il];
         int lds = 0;
-        if (hy->form == PIB_FORM_PARALLEL) {
+        if (hy->form == PIB_FORM_PRENORM) {
+            if (L.loop_in) {       // a walk opens: x <- W [x ; embedding] + this walk's vector
+                RC(HK_CONCAT, 0, 12.0 * Td * Wd, pib_concat_stream(have_x ? cur : nullptr, pend_y, pend_b, T, W, x->cat, st));
+                RC(HK_LOOPIN, mmfl(L.loop_in), mmby(L.loop_in), mm(L.loop_in, x->cat, 2 * W, x->y, W, PIB_EPI_NONE));
+                have_x = false; pend_y = x->y; pend_b = L.loop_step;
+            }
+            if ((rc = prenorm(L.g1, L.shift, L.shift_off, true)) != PIB_OK) return rc;
+            if ((rc = run_mixer(L, x->h)) != PIB_OK) return rc;
+            pend_y = x->y; pend_b = L.o_bias;
+            if (L.mlp == PIB_MLP_XIELU) {
+                if ((rc = prenorm(L.g2, nullptr, 0, true)) != PIB_OK) return rc;
+                RC(HK_UP, mmfl(L.up), mmby(L.up), mm(L.up, x->h, W, x->proj, L.ff, PIB_EPI_NONE));
+                RC(HK_XIELU, 0, 8.0 * Td * L.ff, pib_xielu(x->proj, T, L.ff, L.act[0], L.act[1], st));
+                RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
+                pend_y = x->y; pend_b = nullptr;
+            } else if (L.mlp != PIB_MLP_NONE) { pib_set_error("decode: feed-forward %d in a pre-norm layer", L.mlp); return PIB_ERR_UNSUPP; }
+        } else if (hy->form == PIB_FORM_PARALLEL) {
             // x += mixer(N1 x) + ff(N2 x): both norms in one pass over x, the sum in one pass at the end
             RC(HK_NORM2, 0, (L.mlp ? 12.0 : 8.0) * Td * Wd, pib_rms_norm2(x->x, L.norm1, L.mlp ? L.norm2 : nullptr, eps, 1.0f, T, W, x->h, x->h2, st));
             if ((rc = run_mixer(L, x->h)) != PIB_OK) return rc;
@@ -423,16 +516,20 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             }
         }
         if (const char * dump = getenv("PIB_HYBRID_DUMP")) {          // debugging: the residual stream after every layer, one file per layer and decode
-            std::vector<float> hb((size_t) T * W);
-            cudaMemcpyAsync(hb.data(), x->x, hb.size() * 4, cudaMemcpyDeviceToHost, st);
+            std::vector<float> hb((size_t) T * W), yb, bb;
+            if (!(hy->form == PIB_FORM_PRENORM && !have_x)) cudaMemcpyAsync(hb.data(), hy->form == PIB_FORM_PRENORM ? cur : x->x, hb.size() * 4, cudaMemcpyDeviceToHost, st);
+            if (pend_y) { yb.resize(hb.size()); cudaMemcpyAsync(yb.data(), pend_y, hb.size() * 4, cudaMemcpyDeviceToHost, st); }
+            if (pend_b) { bb.resize((size_t) W); cudaMemcpyAsync(bb.data(), pend_b, (size_t) W * 4, cudaMemcpyDeviceToHost, st); }
             cudaStreamSynchronize(st);
+            for (size_t i = 0; i < hb.size(); i++) hb[i] += (pend_y ? yb[i] : 0.f) + (pend_b ? bb[i % (size_t) W] : 0.f);      // what the next norm's kernel will add
             char path[512];
             snprintf(path, sizeof(path), "%s/d%llu_l%d.f32", dump, (unsigned long long) c->n_decode, il);
             if (FILE * f = fopen(path, "wb")) { fwrite(hb.data(), 4, hb.size(), f); fclose(f); }
         }
     }
-    if (hy->form == PIB_FORM_PARALLEL) RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_rms_norm2(x->x, m->output_norm, nullptr, eps, hy->logit_scale, T, W, x->h, nullptr, st));
-    else                               RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
+    if (hy->form == PIB_FORM_PRENORM)       { if ((rc = prenorm(hy->final_g, nullptr, 0, false)) != PIB_OK) return rc; }
+    else if (hy->form == PIB_FORM_PARALLEL) RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_rms_norm2(x->x, m->output_norm, nullptr, eps, hy->logit_scale, T, W, x->h, nullptr, st));
+    else                                    RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
     RC(HK_HEAD, mmfl(m->output), mmby(m->output), mm(m->output, x->h, W, run.logits, m->n_vocab, PIB_EPI_NONE));
     RC(HK_SAMPLE, 0, 4.0 * Td * m->n_vocab, pib_sample_topk(run.logits, T, m->n_vocab, c->bias_ids_dev, c->bias_val_dev, c->n_bias, run.res_dev, c->desc_dev, c->cancel_table, st));
 #undef RC

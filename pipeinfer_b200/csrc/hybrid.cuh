@@ -2,11 +2,16 @@
 //   mixers:        windowed latent attention with a sink; the gated linear recurrence HGRN2; windowed softmax attention over cached
 //                  key / value heads (grouped queries, short convolutions on q / k / v, per-head query / key norms, value mixing with
 //                  an earlier layer); RWKV-style time mixing (token shift, per-channel decay, bonus for the current token); the gated
-//                  delta rule
-//   feed-forwards: dense with a PolyNorm activation; routed mixtures of experts with a shared expert (softmax or sigmoid router,
+//                  delta rule; the selective state-space scan (Mamba); a two-branch mixer -- softmax attention over chunks with a sink,
+//                  rotated and unit-normed queries / keys, values that are the unrotated keys and a gate per head, beside a linear
+//                  attention with a constant decay per head ("lightning attention") -- whose outputs are summed with two constants
+//   feed-forwards: dense with a PolyNorm or an xIELU activation; routed mixtures of experts with a shared expert (softmax or sigmoid router,
 //                  weights renormalised or not, on the experts' outputs or inputs, relu^2 or clamped gated experts)
-//   layer forms:   sequential with LayerNorm on the sublayers' outputs; parallel with two RMS norms of the same input
-// Designs built from these parts: "Rapisun", "Fabivik".  The parts take their sizes and constants as parameters so that another
+//   layer forms:   sequential with LayerNorm on the sublayers' outputs; parallel with two RMS norms of the same input; sequential
+//                  pre-norm (RMS norm with ONE number as its weight) with a token shift in front of every mixer
+//   layer runs:    a run of layers may be walked several times with the same weights, each walk with a cache and state of its own and
+//                  opened by a projection of [stream ; embedding] plus a learned vector per walk
+// Designs built from these parts: "Rapisun", "Fabivik", "Lulenex".  The parts take their sizes and constants as parameters so that another
 // layer-list design can name them too.
 //
 // What such a model adds to the runtime, beside what llama / falcon graphs use:
@@ -20,11 +25,14 @@
 
 #include "engine.cuh"
 
-enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2, PIB_MIXER_SWA = 3, PIB_MIXER_WKV = 4, PIB_MIXER_DELTA = 5 };
-enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2 };
+enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2, PIB_MIXER_SWA = 3, PIB_MIXER_WKV = 4, PIB_MIXER_DELTA = 5, PIB_MIXER_SSM = 6, PIB_MIXER_DUAL = 7 };
+enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2, PIB_MLP_XIELU = 3 };
+// which earlier positions j a token at p may read: the last `window` ones (p - window < j <= p), or those of its own chunk (j / window == p / window)
+enum { PIB_MASK_WINDOW = 0, PIB_MASK_CHUNK = 1 };
 enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1 };
 // layer forms: x += LN(mixer(conv(x))), x += LN(ff(x))   |   x += mixer(N1(x)) + ff(N2(x)), N = RMS norm with weight (1 + w)
-enum { PIB_FORM_POSTNORM = 0, PIB_FORM_PARALLEL = 1 };
+//              x += mixer(shift(N(x))), x += ff(N(x)), N = RMS norm times one number, shift(h)_t = h_t + (h_{t-1} - h_t) * mu
+enum { PIB_FORM_POSTNORM = 0, PIB_FORM_PARALLEL = 1, PIB_FORM_PRENORM = 2 };
 // mixture of experts: how the router's logits become weights, where a weight multiplies, what an expert computes
 enum { PIB_ROUTE_SOFTMAX_RENORM = 0, PIB_ROUTE_SIGMOID = 1 };
 enum { PIB_EXPERT_RELU2 = 0, PIB_EXPERT_GLU_CLAMP = 1 };
@@ -62,6 +70,29 @@ struct pib_hlayer {
     size_t  shift_off = 0;                            // floats into a slot's state: the previous token's mixer input [width]
     // ---- gated delta rule (PIB_MIXER_DELTA) ----
     float * a_log = nullptr, * dt_bias = nullptr;     // [heads]
+    // ---- a layer of a run that is walked several times: the tensors belong to the first walk's entry (the others point at them) ----
+    int     weights_of = -1;                          // index of the entry that owns this one's tensors (-1: itself)
+    pib_weight * loop_in = nullptr;                   // set on the first layer of a walk: x <- loop_in [x ; embedding] + loop_step
+    float * loop_step = nullptr;                      // [width], this walk's row
+    // ---- pre-norm form: the norms' single weights, the token shift in front of the mixer ----
+    float   g1 = 1.f, g2 = 1.f;
+    float * shift = nullptr;                          // [width]; the previous token's normed row lives at shift_off
+    // ---- selective state-space scan (PIB_MIXER_SSM): S[c][n] <- exp(dt_c A[c][n]) S[c][n] + dt_c u_c B_n, y_c = sum_n S[c][n] C_n + D_c u_c ----
+    int   inner = 0, n_state = 0, dt_rank = 0;        // taps: of the convolution on u
+    pib_weight * ssm_in = nullptr, * ssm_x = nullptr, * ssm_dt = nullptr;   // [2 inner][width]: u | z;  [dt_rank + 2 n_state][inner];  [inner][dt_rank]
+    float * conv_b = nullptr, * ssm_a = nullptr, * ssm_d = nullptr;         // [inner]; A = -exp(A_log) [inner][n_state]; [inner]   (dt_bias: [inner])
+    // ---- two-branch mixer (PIB_MIXER_DUAL) ----
+    // softmax branch: heads / kv_heads / dim (= vdim: the values are the unrotated keys) / rot_dims / rot_base / scale / window + mask / sink;
+    // linear branch: heads2 x (dim2 -> vdim2), decay per head.  qkv holds the rows of every projection of the mixer's input:
+    // q (heads*dim) | k (kv_heads*dim) | head gates (heads) | q2 (heads2*dim2) | k2 (heads2*dim2) | v2 (heads2*vdim2) | gates2 (heads2*vdim2);
+    // wo the columns [softmax branch (heads*dim) | linear branch (heads2*vdim2)]
+    int   mask = PIB_MASK_WINDOW;
+    int   heads2 = 0, dim2 = 0, vdim2 = 0;
+    float * proj_bias = nullptr;                      // [rows of qkv], zeros where a projection has none
+    float * o_bias = nullptr;                         // [width], already times mix_a
+    float * decay = nullptr;                          // [heads2]
+    float   mix_a = 1.f, mix_b = 1.f;                 // mixer = mix_a * softmax branch + mix_b * linear branch
+                                                      // (state_off: the linear branch's matrices [heads2][dim2][vdim2])
     // ---- feed-forward ----
     int   ff = 0;
     pib_weight * up = nullptr, * down = nullptr;
@@ -84,6 +115,10 @@ struct pib_hybrid {
     float * embd_norm = nullptr;
     std::vector<pib_hlayer> layers;
     size_t  state_floats = 0;                         // per state slot
+    float   final_g = 1.f;                            // pre-norm form: the last norm's weight
+    int     loops = 0;                                // 1: some layers open a walk (the embedding rows are kept for the step)
+    pib_weight * loop_in = nullptr;                   // [width][2 width]
+    float * loop_steps = nullptr;                     // [walks][width]
     int     n_cache = 0;
     std::vector<int> cache_row;                       // floats per cell of caching layer i
     struct Rope { float base; int dims; };
@@ -91,6 +126,7 @@ struct pib_hybrid {
     // widest per-token scratch rows over all layers
     int     w_proj = 0, w_cq = 0, w_q = 0, w_lat = 0, w_att = 0, w_pairs = 0, w_eup = 0, w_router = 0;
     int     w_conv = 0, w_vfirst = 0, w_shift = 0;    // convolved q | k | v rows, the first mixing layer's values, the five token-shift mixes
+    int     w_cat = 0;                                // [stream ; embedding] rows of a walk's opening
 };
 
 struct pib_hybrid_ctx;
@@ -136,7 +172,7 @@ int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, f
 int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int W, float * h,
                    cudaStream_t st);
 int pib_chan_conv(const float * u, int ldu, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int C, float * out, int ldo,
-                  int add_input, int silu, cudaStream_t st);
+                  int add_input, int silu, cudaStream_t st, const float * bias = nullptr);
 int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
                     const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st);
 int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
@@ -144,7 +180,7 @@ int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer &
 int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
                             const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, void * P, float * ctx, cudaStream_t st);
 int pib_window_softmax(float * S, void * P, int NKp, int NK, int j0, int window, const int32_t * pos, int t0, int n_rows, int rows_per_z, int rep, const float * sink,
-                       cudaStream_t st);
+                       cudaStream_t st, int mask = PIB_MASK_WINDOW);
 int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * lower, int T, int HD, cudaStream_t st);
 int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, const float * onorm, float eps,
                    float * out, cudaStream_t st);
@@ -169,4 +205,16 @@ int pib_wkv_scan(const float * rkvg, int ld, const float * wdec, int ldw, const 
 int pib_delta_scan(const float * cv, int ldc, const float * bg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st);
 int pib_gated_head_norm(float * o, int T, int H, int V, const float * w, int w_hs, const float * gate, int ldg, float eps, cudaStream_t st);
 int pib_glu_clamp(float * gu, int ld, int F, float limit, const float * scale, const int32_t * scale_of, int n_rows, cudaStream_t st);
+// scan_kernels.cu
+int pib_prenorm_shift(const float * xin, const float * y, const float * bias, float * xout, float g, float eps, const float * mu, const pib_hbatch & b, float * state,
+                      size_t state_stride, size_t shift_off, int W, float * h, cudaStream_t st);
+int pib_embed_pair(const pib_weight * embd, const int32_t * tok, int T, int W, float * x, float * cat, cudaStream_t st);
+int pib_concat_stream(const float * xin, const float * y, const float * bias, int T, int W, float * cat, cudaStream_t st);
+int pib_xielu(float * z, int T, int F, float p, float q, cudaStream_t st);
+int pib_ssm_scan(const float * u, int ldu, const float * dtr, int lddt, const float * bc, int ldbc, const float * z, int ldz, const pib_hlayer & L, const pib_hbatch & b,
+                 float * state, size_t state_stride, float * out, cudaStream_t st);
+int pib_dual_prep(float * proj, int ldp, const pib_hlayer & L, float eps, const pib_hbatch & b, const float2 * rope, float * q, float * cache, int cache_row, cudaStream_t st);
+int pib_decay_scan(const float * proj, int ldp, int q_off, int k_off, int v_off, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out,
+                   cudaStream_t st);
+int pib_dual_gate(const float * a, const float * bo, const float * proj, int ldp, int ga_off, int gb_off, const pib_hlayer & L, float eps, int T, float * out, cudaStream_t st);
 int pib_parallel_sum(float * x, const float * mixer, const float * shared, const float * sgl, int ldsg, const float * edn, const int32_t * inv, int top, int T, int W, cudaStream_t st);

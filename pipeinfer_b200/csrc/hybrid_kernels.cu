@@ -79,19 +79,21 @@ int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, f
 }
 
 // ---- causal convolution with a per-sequence tail ---------------------------------------------------------------------------------
-// out[t][c] = (flags & 1 ? u[t][c] : 0) + sum_j w[c][j] * in(t - taps + 1 + j)[c], then silu if flags & 2; in() is this batch's u inside the
+// out[t][c] = (flags & 1 ? u[t][c] : 0) + (bias ? bias[c] : 0) + sum_j w[c][j] * in(t - taps + 1 + j)[c], then silu if flags & 2; in() is this batch's u inside the
 // token's segment, the slot's tail ([taps-1][C]) before it.  u rows have pitch ldu, out rows pitch ldo; C channels.
 #define CANON_MAX_TAPS 16
 enum { CONV_ADD_INPUT = 1, CONV_SILU = 2 };
 __global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x, int ldu, const float * __restrict__ w, int taps, const int32_t * __restrict__ seg,
                                                     const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot,
-                                                    const float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h, int ldo, int flags) {
+                                                    const float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h, int ldo, int flags,
+                                                    const float * __restrict__ bias) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int t = blockIdx.x, sg = seg[t], s0 = seg_start[sg];
     const float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float acc = (flags & CONV_ADD_INPUT) ? x[(size_t) t * ldu + c] : 0.f;
+        if (bias) acc += bias[c];
         for (int j = 0; j < taps; j++) {
             const int tau = t - (taps - 1) + j;
             const float v = tau >= s0 ? x[(size_t) tau * ldu + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
@@ -125,10 +127,10 @@ __global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restric
 
 // the general form: C channels of rows u (pitch ldu) -> out (pitch ldo); add_input: out += u; silu: activation on the way out
 int pib_chan_conv(const float * u, int ldu, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int C, float * out, int ldo,
-                  int add_input, int silu, cudaStream_t st) {
+                  int add_input, int silu, cudaStream_t st, const float * bias) {
     if (taps > CANON_MAX_TAPS || taps < 1) { pib_set_error("convolution: %d taps (1 to %d)", taps, CANON_MAX_TAPS); return PIB_ERR_UNSUPP; }
     const int flags = (add_input ? CONV_ADD_INPUT : 0) | (silu ? CONV_SILU : 0);
-    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, u, ldu, w, taps, b.seg, b.seg_start, b.seg_slot, (const float *) state, state_stride, tail_off, C, out, ldo, flags);
+    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, u, ldu, w, taps, b.seg, b.seg_start, b.seg_slot, (const float *) state, state_stride, tail_off, C, out, ldo, flags, bias);
     CKL();
     if (taps > 1) { pib_launch(canon_tail_kernel, dim3(b.S), dim3(256), (size_t) (0), st, u, ldu, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, C); CKL(); }
     return PIB_OK;
@@ -344,18 +346,18 @@ __global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict_
         out[R + i] = v * scale;
     }
 }
-// one score row per (token, head), in place: keys outside [p - window + 1, p] and the pad get weight 0, the sink (optional) one share of
+// one score row per (token, head), in place: keys outside [p - window + 1, p] (chunk mask: outside [p - p % window, p]) and the pad get weight 0, the sink (optional) one share of
 // the denominator.  Rows come in groups of rows_per_z (one group per problem of the score matmul), inside a group `rep` heads per token:
 // token t0 + (row % rows_per_z) / rep, head (row / rows_per_z) * rep + (row % rows_per_z) % rep.
 __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S, __nv_bfloat16 * __restrict__ P, int NKp, int NK, int j0, int window,
-                                                          const int32_t * __restrict__ pos, int t0, int rows_per_z, int rep, const float * __restrict__ sink) {
+                                                          const int32_t * __restrict__ pos, int t0, int rows_per_z, int rep, const float * __restrict__ sink, int mask) {
     pib_pdl_wait();
     pib_pdl_trigger();
     __shared__ float red[32];
     const int row = blockIdx.x, rz = row % rows_per_z, t = t0 + rz / rep, h = (row / rows_per_z) * rep + rz % rep, p = pos[t];
     float *   s = S + (size_t) row * NKp;
     __nv_bfloat16 * pw = P + (size_t) row * 2 * NKp;   // [weights' bfloat16 part | what the rounding left]: the value matmul sees both, so the weights keep fp32 accuracy
-    const int lo = max(0, p - window + 1) - j0, hi = p - j0;            // valid columns [lo, hi]
+    const int lo = (mask == PIB_MASK_CHUNK ? p - p % window : max(0, p - window + 1)) - j0, hi = p - j0;            // valid columns [lo, hi]
     const float sk = sink ? sink[h] : -INFINITY;
     float m = sk;
     for (int j = lo + (int) threadIdx.x; j <= hi; j += blockDim.x) m = fmaxf(m, s[j]);
@@ -380,8 +382,8 @@ __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S
     (void) NK; (void) hi;
 }
 int pib_window_softmax(float * S, void * P, int NKp, int NK, int j0, int window, const int32_t * pos, int t0, int n_rows, int rows_per_z, int rep, const float * sink,
-                       cudaStream_t st) {
-    pib_launch(lat_softmax_kernel, dim3(n_rows), dim3(256), (size_t) (0), st, S, (__nv_bfloat16 *) P, NKp, NK, j0, window, pos, t0, rows_per_z, rep, sink);
+                       cudaStream_t st, int mask) {
+    pib_launch(lat_softmax_kernel, dim3(n_rows), dim3(256), (size_t) (0), st, S, (__nv_bfloat16 *) P, NKp, NK, j0, window, pos, t0, rows_per_z, rep, sink, mask);
     CKL();
     return PIB_OK;
 }

@@ -103,11 +103,11 @@ int pib_swa_prep(const float * cv, int ldc, const pib_hlayer & L, float eps, con
 }
 
 // grid (token, head group); a block holds HPB query heads x KS key shares, one warp each.  A warp walks its share of the window
-// [max(0, p - window + 1), p] through the slot's position -> cell table, keeps a running maximum / denominator / weighted sum of value
+// [max(0, p - window + 1), p] (chunk mask: of the token's chunk [p - p % window, p]) through the slot's position -> cell table, keeps a running maximum / denominator / weighted sum of value
 // rows, and the shares of a head are merged in shared memory.  A sink (optional) is one more logit without a row: the running state of
 // share 0 starts at (max = sink, denominator = 1).
 template <int RPL>
-__global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__ q, int H, int G, int D, int V, float scale, int window, const float * __restrict__ sink,
+__global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__ q, int H, int G, int D, int V, float scale, int window, int mask, const float * __restrict__ sink,
                                                       const int32_t * __restrict__ pos, const int32_t * __restrict__ slot, const float * __restrict__ cache, int cache_row,
                                                       const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ out,
                                                       const int32_t * __restrict__ skip) {
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (skip && skip[t]) return;                  // this token's segment goes through the matmul form
     const int hl = warp / KS, ks = warp % KS, h = blockIdx.y * HPB + hl;
-    const int p = pos[t], lo = max(0, p - window + 1);
+    const int p = pos[t], lo = mask == PIB_MASK_CHUNK ? p - p % window : max(0, p - window + 1);
     const bool live = h < H;
     float qv[RPL], acc[RPL];
     float m = -INFINITY, l = 0.f;
@@ -181,7 +181,7 @@ int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b
     const int threads = HPB * KS * 32;
 #define KA_GO(RPL) do {                                                                                                              \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kv_attn_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);   \
-        pib_launch(kv_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) smem, st, q, H, L.kv_heads, L.dim, V, L.scale, L.window, (const float *) L.sink, b.pos, b.slot, cache, \
+        pib_launch(kv_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) smem, st, q, H, L.kv_heads, L.dim, V, L.scale, L.window, L.mask, (const float *) L.sink, b.pos, b.slot, cache, \
                    cache_row, cellmap, n_ctx, HPB, KS, out, skip);                                                                  \
     } while (0)
     if (R <= 32) KA_GO(1); else if (R <= 64) KA_GO(2); else if (R <= 128) KA_GO(4); else if (R <= 256) KA_GO(8); else if (R <= 512) KA_GO(16);
@@ -250,7 +250,7 @@ int pib_kv_attention_mm(const float * q, const pib_hlayer & L, const pib_hbatch 
     a.Y = S; a.ldy = NKp; a.yz = (int64_t) M * NKp; a.M = M; a.N = NK; a.K = 3 * D; a.Z = G;
     int rc = pib_dense_mm(a, st);
     if (rc != PIB_OK) return rc;
-    if ((rc = pib_window_softmax(S, P, NKp, NK, j0, L.window, b.pos, t0, G * M, M, rep, L.sink, st)) != PIB_OK) return rc;
+    if ((rc = pib_window_softmax(S, P, NKp, NK, j0, L.window, b.pos, t0, G * M, M, rep, L.sink, st, L.mask)) != PIB_OK) return rc;
     pib_mm v;
     v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.wz = (int64_t) V * 2 * NKp; v.X = (const float *) P; v.ldx = 2 * NKp; v.xz = (int64_t) M * 2 * NKp; v.x_bf16 = 1;
     v.Y = Qc; v.ldy = V; v.yz = (int64_t) M * V; v.M = M; v.N = V; v.K = 2 * NKp; v.Z = G;               // the query rows are used up: the outputs take their place
@@ -349,6 +349,7 @@ int pib_delta_prep(float * cv, int ldc, const pib_hlayer & L, const float * proj
 //   MODE 0 (time mixing):  o = sum_d a_d (s_d + u_d k_d v),  s_d <- w_d s_d + k_d v                         row = [a D | k D | w D | v LS_VT | dot]
 //   MODE 1 (delta rule):   s_d <- g s_d,  e = beta (v - sum_d s_d k_d),  o = sum_d s_d a_d + e sum_d k_d a_d,  s_d <- s_d + k_d e
 //                                                                                                           row = [a D | k D | v LS_VT | g, beta | dot]
+//   MODE 2 (constant decay): s_d <- c s_d + k_d v,  o = sum_d a_d s_d  (read after the write; c one number per head)   row = [a D | k D | v LS_VT | dot]
 // What does not depend on the matrix or the column -- dot = sum_d a_d u_d k_d (MODE 0), sum_d a_d k_d (MODE 1) -- is formed once per token
 // when its chunk has landed; in MODE 1 the read-out is taken from the sums over the matrix before the write (one round of shuffles for
 // both sums), and the next token's rows are already in registers while the sums of this one cross the lanes.
@@ -357,7 +358,7 @@ int pib_delta_prep(float * cv, int ldc, const pib_hlayer & L, const float * proj
 struct ls_args {
     const float * a; int lda, a_hs;          // query-like rows: a[t * lda + group * a_hs + d]
     const float * k; int ldk, k_hs;
-    const float * w; int ldw;                // MODE 0: decay rows w[t * ldw + h * D + d];   MODE 1: bg rows [beta (H) | g (H)], ldw = 2 H
+    const float * w; int ldw;                // MODE 0: decay rows w[t * ldw + h * D + d];   MODE 1: bg rows [beta (H) | g (H)], ldw = 2 H;   MODE 2: decay [H]
     const float * v; int ldv;                // v[t * ldv + h * V + j]
     const float * u;                         // MODE 0: bonus [H][D]
     int H, G, D, V, chunk;
@@ -380,7 +381,8 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
     const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LS_VT, part = threadIdx.x & 15, vl = threadIdx.x >> 4, vd = v0 + vl;
     const int D = FULL ? 16 * RPT : A.D, V = A.V, H = A.H, grp = h / (H / A.G), CH = A.chunk;
     const int s0 = A.seg_start[sg], n = A.seg_len[sg];
-    const int vbase = MODE == 0 ? 3 * D : 2 * D, dot_off = vbase + LS_VT + (MODE == 0 ? 0 : 2), row_f = dot_off + 1;
+    const int vbase = MODE == 0 ? 3 * D : 2 * D, dot_off = vbase + LS_VT + (MODE == 1 ? 2 : 0), row_f = dot_off + 1;
+    const float cdec = MODE == 2 ? A.w[h] : 0.f;
     const bool vok = vd < V;
     float * S = A.state + (size_t) A.seg_slot[sg] * A.state_stride + A.state_off + (size_t) h * D * V;
     float s[RPT], ub[RPT];
@@ -456,6 +458,17 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
                 }
                 acc = ls_sum16(acc);
                 if (part == 0 && vok) *op = fmaf(v, dot, acc);
+            } else if (MODE == 2) {
+                float acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; r++) { acc = fmaf(aa[r], s[r], acc); s[r] = fmaf(cdec, s[r], kk[r] * v); }
+#pragma unroll
+                for (int r = 0; r < RPT; r++) {
+                    const bool ok = FULL || part + 16 * r < D;
+                    an[r] = ok ? qn[16 * r] : 0.f; kn[r] = ok ? qn[D + 16 * r] : 0.f; wn[r] = 0.f;
+                }
+                acc = ls_sum16(acc);
+                if (part == 0 && vok) *op = fmaf(cdec, acc, v * dot);       // sum_d a_d (c s_d + k_d v)
             } else {
                 const float g = sc[LS_VT], beta = sc[LS_VT + 1];
                 float sk = 0.f, sa = 0.f;
@@ -486,7 +499,7 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
 static int lin_scan(int mode, ls_args & A, int S, cudaStream_t st) {
     if (A.D > 256) { pib_set_error("recurrence: dim %d not supported (up to 256)", A.D); return PIB_ERR_UNSUPP; }
     dim3 grid((unsigned) S, (unsigned) A.H, (unsigned) ((A.V + LS_VT - 1) / LS_VT));
-    const size_t row_f = (size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + (mode == 0 ? 0 : 2) + 1;
+    const size_t row_f = (size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + (mode == 1 ? 2 : 0) + 1;
     // chunks of 32 tokens halve the barriers per token, but their double buffer must not push part of the grid into a second wave
     const size_t smem32 = row_f * 4 * 2 * 32;
     const size_t per_sm = smem32 <= 100 * 1024 ? (size_t) (227 * 1024) / (smem32 + 1024) : 0;
@@ -496,7 +509,7 @@ static int lin_scan(int mode, ls_args & A, int S, cudaStream_t st) {
                                     pib_launch(lin_scan_kernel<RPT, MODE, FULL>, dim3(grid), dim3(16 * LS_VT), (size_t) smem, st, A); } while (0)
 #define LS_PICK(MODE) do { if (A.D == 64) LS_GO(4, MODE, true); else if (A.D == 128) LS_GO(8, MODE, true); else if (A.D <= 32) LS_GO(2, MODE, false); \
                            else if (A.D <= 64) LS_GO(4, MODE, false); else if (A.D <= 128) LS_GO(8, MODE, false); else LS_GO(16, MODE, false); } while (0)
-    if (mode == 0) LS_PICK(0); else LS_PICK(1);
+    if (mode == 0) LS_PICK(0); else if (mode == 1) LS_PICK(1); else LS_PICK(2);
 #undef LS_PICK
 #undef LS_GO
     CKL();
@@ -520,6 +533,16 @@ int pib_delta_scan(const float * cv, int ldc, const float * bg, const pib_hlayer
     A.H = L.heads; A.G = L.kv_heads; A.D = L.dim; A.V = L.vdim; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
     A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
     return lin_scan(1, A, b.S, st);
+}
+
+// linear attention with one constant decay per head: rows proj[t] hold q (H*D) at q_off, k (H*D) at k_off, v (H*V) at v_off, activations applied
+int pib_decay_scan(const float * proj, int ldp, int q_off, int k_off, int v_off, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out,
+                   cudaStream_t st) {
+    ls_args A;
+    A.a = proj + q_off; A.lda = ldp; A.a_hs = L.dim2; A.k = proj + k_off; A.ldk = ldp; A.k_hs = L.dim2; A.w = L.decay; A.ldw = 0; A.v = proj + v_off; A.ldv = ldp; A.u = nullptr;
+    A.H = L.heads2; A.G = L.heads2; A.D = L.dim2; A.V = L.vdim2; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
+    A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
+    return lin_scan(2, A, b.S, st);
 }
 
 // one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w[(h * w_hs) + i] * silu(gate[t * ldg + h * V + i])

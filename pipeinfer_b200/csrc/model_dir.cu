@@ -532,9 +532,182 @@ static pib_model * build_fabivik(const Json & cfg, TensorSource & src, int dtype
     return mp.release();
 }
 
+// ---- the Lulenex builder ----------------------------------------------------------------------------------------------------------
+// Sequential pre-norm layers (RMS norms whose weight is one number, a token shift in front of every mixer), mixers "mamba1" (selective
+// state-space scan) and "parallel" (chunked softmax attention with a sink beside a linear attention with constant decays), dense xIELU
+// feed-forwards, and a "loop": layers start .. stop-1 are walked `times` times with the same tensors.  The list the runtime walks holds one
+// entry per layer RUN: entries of later walks point at the first walk's tensors and own only their cache rows and state.
+// Tensor names: '<layer>.norm1|norm2|shift', '<layer>.mix.*', '<layer>.mlp.*', 'loop.in', 'loop.step', 'final.norm', 'embed', 'head'.
+static pib_model * build_lulenex(const Json & cfg, TensorSource & src, int dtype) {
+    std::unique_ptr<pib_model, void (*)(pib_model *)> mp(new pib_model(), pib_model_free);
+    pib_model * m = mp.get();
+    pib_hybrid * hy = new pib_hybrid();
+    m->hy = hy;
+    m->arch = 2; m->name = "Lulenex";
+    bool ok = true;
+    const int W = (int) jnum(&cfg, "width", 0, &ok), V = (int) jnum(&cfg, "vocab", 0, &ok);
+    const Json * layers = cfg.get("layers");
+    if (!ok || W <= 0 || V <= 0 || !layers || layers->kind != Json::ARR || layers->arr.empty()) { pib_set_error("model: config.json needs width, vocab and layers"); return nullptr; }
+    const int n_base = (int) layers->arr.size();
+    hy->dtype = dtype;
+    hy->form = PIB_FORM_PRENORM;
+    hy->eps = (float) jnum(cfg.get("norm"), "eps", 1e-6);
+    hy->taps = 0;
+    m->n_embd = W; m->n_vocab = V; m->layer_begin = 0;
+    m->wtype = dtype; m->n_ctx_train = 1 << 20; m->n_head = 1; m->n_head_kv = 1; m->tok_bos = -1; m->tok_eos = -1;
+    std::vector<float> v;
+#define GET(name, ...) do { if (!src.get((name), { __VA_ARGS__ }, v)) return nullptr; } while (0)
+#define VEC(dst, name, n) do { GET(name, (int64_t) (n)); if (!((dst) = upload_f32v(v))) return nullptr; } while (0)
+#define MAT(dst, name, N, K) do { GET(name, (int64_t) (N), (int64_t) (K)); if (!((dst) = upload_mat(v, (N), (K), dtype, m))) return nullptr; } while (0)
+#define APPEND(all, name, N, K) do { GET(name, (int64_t) (N), (int64_t) (K)); (all).insert((all).end(), v.begin(), v.end()); } while (0)
+#define ONE(dst, name) do { GET(name); (dst) = v[0]; } while (0)
+    MAT(m->tok_embd, "embed", V, W);
+    ONE(hy->final_g, "final.norm");
+    MAT(m->output, "head", V, W);
+    // the walked run
+    int lp_start = 0, lp_stop = 0, lp_times = 0;
+    const Json * lp = cfg.get("loop");
+    if (lp && !lp->is_null()) {
+        lp_start = (int) jnum(lp, "start", 0); lp_stop = (int) jnum(lp, "stop", 0); lp_times = (int) jnum(lp, "times", 1);
+        if (lp_start < 0 || lp_stop <= lp_start || lp_stop > n_base || lp_times < 1) { pib_set_error("model: loop start %d, stop %d, times %d over %d layers", lp_start, lp_stop, lp_times, n_base); return nullptr; }
+        hy->loops = 1;
+        MAT(hy->loop_in, "loop.in", W, 2 * (int64_t) W);
+        GET("loop.step", (int64_t) lp_times, (int64_t) W);
+        if (!(hy->loop_steps = upload_f32v(v))) return nullptr;
+        hy->w_cat = 2 * W;
+    }
+    auto widen = [](int & a, int64_t b) { if (b > a) a = (int) b; };
+    // ---- the layers as the file holds them ----
+    std::vector<pib_hlayer> base((size_t) n_base);
+    for (int il = 0; il < n_base; il++) {
+        const Json & jl = layers->arr[il];
+        pib_hlayer & L = base[il];
+        const std::string p = "l" + std::to_string(il) + ".", px = p + "mix.", pm = p + "mlp.";
+        const Json * ty = jl.get("type"), * mx = jl.get("mixer"), * ml = jl.get("mlp");
+        if (!ty || ty->kind != Json::STR || !mx) { pib_set_error("model: layer %d needs type and mixer", il); return nullptr; }
+        ONE(L.g1, p + "norm1");
+        VEC(L.shift, p + "shift", W);
+        if (ty->str == "mamba1") {
+            L.mixer = PIB_MIXER_SSM;
+            L.inner = (int) jnum(mx, "inner", 0); L.n_state = (int) jnum(mx, "state", 0); L.dt_rank = (int) jnum(mx, "dt_rank", 0); L.taps = (int) jnum(mx, "conv", 1);
+            if (L.inner <= 0 || L.n_state <= 0 || L.dt_rank <= 0 || L.taps < 1) { pib_set_error("model: layer %d: inner / state / dt_rank / conv", il); return nullptr; }
+            const int64_t I = L.inner, N = L.n_state, R = L.dt_rank;
+            MAT(L.ssm_in, px + "in", 2 * I, W);
+            GET(px + "conv", I, (int64_t) L.taps);
+            if (!(L.conv = upload_f32v(v))) return nullptr;
+            VEC(L.conv_b, px + "conv.b", I);
+            MAT(L.ssm_x, px + "x", R + 2 * N, I);
+            MAT(L.ssm_dt, px + "dt", I, R);
+            VEC(L.dt_bias, px + "dt.b", I);
+            GET(px + "A_log", I, N);
+            for (float & a : v) a = (float) -exp((double) a);                  // A = -exp(A_log)
+            if (!(L.ssm_a = upload_f32v(v))) return nullptr;
+            VEC(L.ssm_d, px + "D", I);
+            MAT(L.wo, px + "o", W, I);
+            widen(hy->w_proj, 2 * I); widen(hy->w_conv, I); widen(hy->w_cq, (R + 2 * N + 3) & ~(int64_t) 3); widen(hy->w_lat, I); widen(hy->w_att, I);
+        } else if (ty->str == "parallel") {
+            L.mixer = PIB_MIXER_DUAL;
+            const Json * a = mx->get("left"), * b = mx->get("right");
+            if (!a || !b) { pib_set_error("model: layer %d: the mixer needs left and right", il); return nullptr; }
+            L.heads = (int) jnum(a, "heads", 0); L.kv_heads = (int) jnum(a, "kv_heads", L.heads); L.dim = (int) jnum(a, "dim", 0); L.vdim = (int) jnum(a, "vdim", L.dim);
+            if (L.heads <= 0 || L.dim <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) { pib_set_error("model: layer %d: left heads / kv_heads / dim", il); return nullptr; }
+            if (L.vdim != L.dim) { pib_set_error("model: layer %d: the values are the keys, so vdim (%d) must equal dim (%d)", il, L.vdim, L.dim); return nullptr; }
+            L.scale = (float) jnum(a, "scale", 1.0 / sqrt((double) L.dim));
+            const Json * mk = a->get("mask"), * rt = a->get("rot");
+            L.window = mk && !mk->is_null() ? (int) jnum(mk, "size", 0) : 0;
+            if (L.window > 0) L.mask = PIB_MASK_CHUNK; else L.window = 1 << 30;             // no mask: every earlier token is seen
+            L.rot_base = (float) jnum(rt, "base", 10000.0); L.rot_dims = rt && !rt->is_null() ? (int) jnum(rt, "dims", L.dim) : 0;
+            if (L.rot_dims < 0 || L.rot_dims > L.dim || (L.rot_dims & 1)) { pib_set_error("model: layer %d: rot.dims %d of %d", il, L.rot_dims, L.dim); return nullptr; }
+            L.heads2 = (int) jnum(b, "heads", 0); L.dim2 = (int) jnum(b, "dim", 0); L.vdim2 = (int) jnum(b, "vdim", L.dim2);
+            const Json * dc = b->get("decay");
+            if (L.heads2 <= 0 || L.dim2 <= 0 || L.vdim2 <= 0 || !dc || dc->kind != Json::ARR || (int) dc->arr.size() != L.heads2) { pib_set_error("model: layer %d: right heads / dim / vdim / decay", il); return nullptr; }
+            L.mix_a = (float) jnum(mx, "left_scale", 1.0); L.mix_b = (float) jnum(mx, "right_scale", 1.0);
+            const int64_t H = L.heads, G = L.kv_heads, D = L.dim, H2 = L.heads2, D2 = L.dim2, V2 = L.vdim2;
+            const int64_t rows = (H + G) * D + H + 2 * H2 * D2 + 2 * H2 * V2;
+            std::vector<float> all, bias((size_t) rows, 0.f);
+            APPEND(all, px + "left.q", H * D, W); APPEND(all, px + "left.k", G * D, W); APPEND(all, px + "left.g", H, W);
+            APPEND(all, px + "right.q", H2 * D2, W); APPEND(all, px + "right.k", H2 * D2, W); APPEND(all, px + "right.v", H2 * V2, W); APPEND(all, px + "right.g", H2 * V2, W);
+            if (!(L.qkv = upload_mat(all, rows, W, dtype, m))) return nullptr;
+            GET(px + "left.q.b", H * D); std::copy(v.begin(), v.end(), bias.begin());
+            GET(px + "left.k.b", G * D); std::copy(v.begin(), v.end(), bias.begin() + H * D);
+            if (!(L.proj_bias = upload_f32v(bias))) return nullptr;
+            VEC(L.sink, px + "left.sink", H);
+            {   // one output matrix over the columns [softmax branch | linear branch]
+                std::vector<float> lo, ro;
+                GET(px + "left.o", W, H * D); lo = v;
+                GET(px + "right.o", W, H2 * V2); ro = v;
+                const int64_t Kc = H * D + H2 * V2;
+                all.assign((size_t) (W * Kc), 0.f);
+                for (int64_t r = 0; r < W; r++) {
+                    std::copy(lo.begin() + r * H * D, lo.begin() + (r + 1) * H * D, all.begin() + r * Kc);
+                    std::copy(ro.begin() + r * H2 * V2, ro.begin() + (r + 1) * H2 * V2, all.begin() + r * Kc + H * D);
+                }
+                if (!(L.wo = upload_mat(all, W, Kc, dtype, m))) return nullptr;
+                GET(px + "left.o.b", W);
+                for (float & x : v) x *= L.mix_a;
+                if (!(L.o_bias = upload_f32v(v))) return nullptr;
+                widen(hy->w_att, Kc);
+            }
+            VEC(L.onorm, px + "right.norm", H2 * V2);
+            v.resize((size_t) H2);
+            for (int64_t h = 0; h < H2; h++) v[(size_t) h] = (float) dc->arr[(size_t) h].num;
+            if (!(L.decay = upload_f32v(v))) return nullptr;
+            widen(hy->w_proj, (rows + 3) & ~(int64_t) 3); widen(hy->w_q, H * D); widen(hy->w_lat, H * D); widen(hy->w_conv, H2 * V2);
+        } else { pib_set_error("model: layer %d: unknown mixer '%s'", il, ty->str.c_str()); return nullptr; }
+        if (ml && !ml->is_null()) {
+            const Json * kind = ml->get("kind");
+            if (!kind || kind->str != "dense") { pib_set_error("model: layer %d: unknown mlp kind", il); return nullptr; }
+            L.mlp = PIB_MLP_XIELU; L.ff = (int) jnum(ml, "ff", 0);
+            if (L.ff <= 0) { pib_set_error("model: layer %d: mlp.ff", il); return nullptr; }
+            ONE(L.g2, p + "norm2");
+            MAT(L.up, pm + "up", L.ff, W);
+            MAT(L.down, pm + "down", W, L.ff);
+            GET(pm + "act", 2);
+            L.act[0] = v[0]; L.act[1] = v[1];
+            widen(hy->w_proj, L.ff);
+        }
+    }
+    // ---- the runs: each with cache rows and state of its own ----
+    std::vector<std::pair<int, int>> order;                                       // (layer, walk or -1)
+    for (int il = 0; il < (hy->loops ? lp_start : n_base); il++) order.push_back({ il, -1 });
+    if (hy->loops) {
+        for (int r = 0; r < lp_times; r++) for (int il = lp_start; il < lp_stop; il++) order.push_back({ il, r });
+        for (int il = lp_stop; il < n_base; il++) order.push_back({ il, -1 });
+    }
+    std::vector<int> first((size_t) n_base, -1);
+    size_t state = 0;
+    for (size_t ir = 0; ir < order.size(); ir++) {
+        const int il = order[ir].first, walk = order[ir].second;
+        pib_hlayer L = base[(size_t) il];
+        if (first[(size_t) il] >= 0) L.weights_of = first[(size_t) il]; else first[(size_t) il] = (int) ir;
+        if (walk >= 0 && il == lp_start) { L.loop_in = hy->loop_in; L.loop_step = hy->loop_steps + (size_t) walk * W; }
+        L.shift_off = state; state += (size_t) W;
+        if (L.mixer == PIB_MIXER_SSM) {
+            L.tail_off = state; state += (size_t) (L.taps - 1) * L.inner;
+            L.state_off = state; state += (size_t) L.inner * L.n_state;
+        } else {
+            L.state_off = state; state += (size_t) L.heads2 * L.dim2 * L.vdim2;
+            L.cache_id = hy->n_cache++;
+            hy->cache_row.push_back(2 * L.kv_heads * L.dim);
+            L.rope_id = -1;
+            for (size_t i = 0; i < hy->ropes.size(); i++) if (hy->ropes[i].base == L.rot_base && hy->ropes[i].dims == L.rot_dims) L.rope_id = (int) i;
+            if (L.rope_id < 0) { L.rope_id = (int) hy->ropes.size(); hy->ropes.push_back({ L.rot_base, L.rot_dims }); }
+        }
+        hy->layers.push_back(L);
+    }
+    m->n_layer = (int) hy->layers.size(); m->layer_end = m->n_layer;
+    hy->state_floats = state ? state : 4;
+#undef GET
+#undef VEC
+#undef MAT
+#undef APPEND
+#undef ONE
+    return mp.release();
+}
+
 // ---- registry: config.json "architecture" -> builder ---------------------------------------------------------------------------------
 struct DirArch { const char * name; pib_model * (*build)(const Json &, TensorSource &, int); };
-static const DirArch DIR_ARCHS[] = { { "Rapisun", build_rapisun }, { "Fabivik", build_fabivik } };
+static const DirArch DIR_ARCHS[] = { { "Rapisun", build_rapisun }, { "Fabivik", build_fabivik }, { "Lulenex", build_lulenex } };
 
 static pib_model * build_from_config(const Json & cfg, TensorSource & src, int dtype) {
     const Json * a = cfg.get("architecture");
@@ -569,11 +742,15 @@ void pib_hybrid_model_free(pib_model * m) {
     pib_hybrid * hy = m->hy;
     if (!hy) return;
     for (pib_hlayer & L : hy->layers) {
+        if (L.weights_of >= 0) continue;                  // a later walk of the same layer: the tensors are the first walk's
         for (float * f : { L.norm1, L.norm2, L.canon, L.dq_norm, L.dkv_norm, L.sink, L.f_bias, L.lower, L.onorm, L.conv, L.q_norm, L.k_norm, L.mu, L.w0, L.bonus, L.a_log,
-                           L.dt_bias }) if (f) cudaFree(f);
-        for (pib_weight * w : { L.dqkv, L.uq, L.ukT, L.uv, L.wo, L.qfv, L.up, L.down, L.e_up, L.e_down, L.router, L.s_up, L.s_down, L.qkv, L.rkvg, L.w1, L.w2 }) if (w) pib_weight_free(w);
+                           L.dt_bias, L.shift, L.conv_b, L.ssm_a, L.ssm_d, L.proj_bias, L.o_bias, L.decay }) if (f) cudaFree(f);
+        for (pib_weight * w : { L.dqkv, L.uq, L.ukT, L.uv, L.wo, L.qfv, L.up, L.down, L.e_up, L.e_down, L.router, L.s_up, L.s_down, L.qkv, L.rkvg, L.w1, L.w2, L.ssm_in, L.ssm_x,
+                                L.ssm_dt }) if (w) pib_weight_free(w);
     }
     if (hy->embd_norm) cudaFree(hy->embd_norm);
+    if (hy->loop_in) pib_weight_free(hy->loop_in);
+    if (hy->loop_steps) cudaFree(hy->loop_steps);
     delete hy;
     m->hy = nullptr;
 }

@@ -1,0 +1,321 @@
+// scan_kernels.cu -- more parts for layer-list models (hybrid.cuh), all fp32:
+//
+//   the pre-norm frame: the residual sum, an RMS norm whose weight is ONE number and the token shift h_t + (h_{t-1} - h_t) * mu in one
+//       pass; embedding rows kept beside the stream for layers that are walked again; the opening [stream ; embedding] of a walk
+//   xIELU: z > 0: a z^2 + z/2;  z <= 0: b (exp(z) - 1 - z) + z/2   (a = softplus(p), b = 1/2 + softplus(q))
+//   the selective state-space scan: per channel c and state n  S <- exp(dt_c A[c][n]) S + dt_c u_c B_n,  y_c = sum_n S C_n + D_c u_c,
+//       dt = softplus(raw + bias), the output gated by silu(z)
+//   the two-branch mixer's per-token work: biases, rotation ("rotate half" pairing) of the first rot_dims coordinates of every query /
+//       key head, unit RMS per head, cache write [key | unrotated key as the value], silu on the linear branch's q | k | v; and after
+//       both branches: head gates on the softmax branch, RMS norm over all heads times sigmoid gates on the linear branch, both
+//       scaled into one row for the shared output matmul
+#include "hybrid.cuh"
+
+#include <cuda_bf16.h>
+
+#define CKL() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) { pib_set_error("%s:%d: launch failed: %s", __FILE__, __LINE__, cudaGetErrorString(e__)); return PIB_ERR_CUDA; } } while (0)
+
+__device__ __forceinline__ float sk_block_sum(float v, float * red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; i++) t += red[i];
+    return t;
+}
+__device__ __forceinline__ float sk_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sk_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sk_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ---- the pre-norm frame ------------------------------------------------------------------------------------------------------------
+// x'[t] = (xin ? xin[t] : 0) + (y ? y[t] : 0) + (bias ? bias : 0), stored to xout when xout is given (a buffer other than xin: the block of
+// token t + 1 forms x'[t] from the same inputs).  n[t] = x'[t] / sqrt(mean(x'[t]^2) + eps) * g.  Without mu h[t] = n[t]; with mu
+// h[t] = n[t] + (n[t - 1] - n[t]) * mu, where n[t - 1] of a segment's first token is the slot's row (zeros at a sequence's start).
+__global__ void __launch_bounds__(256) prenorm_shift_kernel(const float * __restrict__ xin, const float * __restrict__ y, const float * __restrict__ bias, float * __restrict__ xout,
+                                                            float g, float eps, const float * __restrict__ mu, const int32_t * __restrict__ seg,
+                                                            const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot, const float * __restrict__ state,
+                                                            size_t state_stride, size_t shift_off, int W, float * __restrict__ h) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float srow[];               // [2][W]: this token's row, the previous token's
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const bool inside = mu && t > seg_start[seg[t]];        // the previous token is in this batch
+    float s0 = 0.f, s1 = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = bias ? bias[i] : 0.f, u = v;
+        if (xin) { v += xin[(size_t) t * W + i]; if (inside) u += xin[(size_t) (t - 1) * W + i]; }
+        if (y)   { v += y[(size_t) t * W + i];   if (inside) u += y[(size_t) (t - 1) * W + i]; }
+        srow[i] = v; srow[W + i] = u;
+        s0 = fmaf(v, v, s0); s1 = fmaf(u, u, s1);
+        if (xout) xout[(size_t) t * W + i] = v;
+    }
+    const float inv0 = g / sqrtf(sk_block_sum(s0, red) / W + eps);
+    float inv1 = 0.f;
+    if (inside) inv1 = g / sqrtf(sk_block_sum(s1, red) / W + eps);
+    const float * prev = mu ? state + (size_t) seg_slot[seg[t]] * state_stride + shift_off : nullptr;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float n = srow[i] * inv0;
+        float o = n;
+        if (mu) { const float pn = inside ? srow[W + i] * inv1 : prev[i]; o = fmaf(pn - n, mu[i], n); }
+        h[(size_t) t * W + i] = o;
+    }
+}
+// after prenorm_shift_kernel: the normed (unshifted) row of every segment's last token becomes its slot's previous row
+__global__ void __launch_bounds__(256) prenorm_tail_kernel(const float * __restrict__ xin, const float * __restrict__ y, const float * __restrict__ bias, float g, float eps,
+                                                           const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot,
+                                                           float * __restrict__ state, size_t state_stride, size_t shift_off, int W) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float srow[];
+    __shared__ float red[32];
+    const int sg = blockIdx.x, t = seg_start[sg] + seg_len[sg] - 1;
+    float s0 = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = bias ? bias[i] : 0.f;
+        if (xin) v += xin[(size_t) t * W + i];
+        if (y)   v += y[(size_t) t * W + i];
+        srow[i] = v;
+        s0 = fmaf(v, v, s0);
+    }
+    const float inv0 = g / sqrtf(sk_block_sum(s0, red) / W + eps);
+    float * dst = state + (size_t) seg_slot[sg] * state_stride + shift_off;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = srow[i] * inv0;
+}
+int pib_prenorm_shift(const float * xin, const float * y, const float * bias, float * xout, float g, float eps, const float * mu, const pib_hbatch & b, float * state,
+                      size_t state_stride, size_t shift_off, int W, float * h, cudaStream_t st) {
+    if (xout && xout == xin) { pib_set_error("pre-norm: the updated stream needs a buffer of its own"); return PIB_ERR_ARG; }
+    pib_launch(prenorm_shift_kernel, dim3(b.T), dim3(256), (size_t) 2 * W * 4, st, xin, y, bias, xout, g, eps, mu, b.seg, b.seg_start, b.seg_slot, (const float *) state, state_stride,
+               shift_off, W, h);
+    CKL();
+    if (mu) {
+        pib_launch(prenorm_tail_kernel, dim3(b.S), dim3(256), (size_t) W * 4, st, xin, y, bias, g, eps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, shift_off, W);
+        CKL();
+    }
+    return PIB_OK;
+}
+
+// x[t] = embedding row of tok[t]; with cat ([T][2 W]) the row is also kept in cat's second half
+template <typename WT>
+__global__ void __launch_bounds__(256) embed_pair_kernel(const WT * __restrict__ embd, const int32_t * __restrict__ tok, int W, float * __restrict__ x, float * __restrict__ cat) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const WT * r = embd + (size_t) tok[blockIdx.x] * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = (float) r[i];
+        x[(size_t) blockIdx.x * W + i] = v;
+        if (cat) cat[(size_t) blockIdx.x * 2 * W + W + i] = v;
+    }
+}
+int pib_embed_pair(const pib_weight * embd, const int32_t * tok, int T, int W, float * x, float * cat, cudaStream_t st) {
+    if (embd->type == PIB_TYPE_BF16) pib_launch(embed_pair_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t) 0, st, (const __nv_bfloat16 *) embd->base, tok, W, x, cat);
+    else                             pib_launch(embed_pair_kernel<float>, dim3(T), dim3(256), (size_t) 0, st, (const float *) embd->base, tok, W, x, cat);
+    CKL();
+    return PIB_OK;
+}
+// cat[t][0 .. W) = xin[t] + y[t] + bias (each optional): the stream as a walk's opening reads it, beside the embedding row
+__global__ void __launch_bounds__(256) concat_stream_kernel(const float * __restrict__ xin, const float * __restrict__ y, const float * __restrict__ bias, int W, float * __restrict__ cat) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = bias ? bias[i] : 0.f;
+        if (xin) v += xin[t * W + i];
+        if (y)   v += y[t * W + i];
+        cat[t * 2 * W + i] = v;
+    }
+}
+int pib_concat_stream(const float * xin, const float * y, const float * bias, int T, int W, float * cat, cudaStream_t st) {
+    pib_launch(concat_stream_kernel, dim3(T), dim3(256), (size_t) 0, st, xin, y, bias, W, cat);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- xIELU, in place on rows [T][F] ----------------------------------------------------------------------------------------------------
+__global__ void xielu_kernel(float * __restrict__ z, int64_t n, float a, float b) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = z[i];
+    z[i] = v > 0.f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v);
+}
+int pib_xielu(float * z, int T, int F, float p, float q, cudaStream_t st) {
+    const int64_t n = (int64_t) T * F;
+    if (n <= 0) return PIB_OK;
+    const double sp = p > 20 ? p : log1p(exp((double) p)), sq = q > 20 ? q : log1p(exp((double) q));
+    pib_launch(xielu_kernel, dim3((unsigned) ((n + 255) / 256)), dim3(256), (size_t) 0, st, z, n, (float) sp, (float) (0.5 + sq));
+    CKL();
+    return PIB_OK;
+}
+
+// ---- selective state-space scan --------------------------------------------------------------------------------------------------------
+// grid (segment, tile of SS_CH channels), SS_CH * SS_P threads: the SS_P lanes of a channel keep states part, part + SS_P, ... in
+// registers.  A chunk of SS_TC tokens is staged in shared memory (dt with its bias and softplus applied once per channel and token),
+// walked token by token, and its outputs leave in whole rows.  The states are read from the slot at the segment's start and left there
+// at its end.
+#define SS_CH 32
+#define SS_P  4
+#define SS_TC 16
+struct ss_args {
+    const float * u; int ldu;                // after convolution and silu
+    const float * dtr; int lddt;             // W_dt (.) before bias and softplus
+    const float * bc; int ldbc;              // [B (N) | C (N)]
+    const float * z; int ldz;                // gate rows
+    const float * dt_bias, * A, * Dk;        // [inner], [inner][N] (negative), [inner]
+    int inner, N;
+    const int32_t * seg_start, * seg_len, * seg_slot;
+    float * state; size_t state_stride, state_off;
+    float * out;                             // [T][inner]
+};
+template <int NPL>
+__global__ void __launch_bounds__(SS_CH * SS_P) ssm_scan_kernel(ss_args a) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float sm[];
+    const int N = a.N, sg = blockIdx.x, c0 = blockIdx.y * SS_CH, cl = threadIdx.x / SS_P, part = threadIdx.x % SS_P, c = c0 + cl;
+    float * dts = sm, * us = dts + SS_TC * SS_CH, * zs = us + SS_TC * SS_CH, * ys = zs + SS_TC * SS_CH, * Bs = ys + SS_TC * SS_CH, * Cs = Bs + SS_TC * N;
+    const int s0 = a.seg_start[sg], n = a.seg_len[sg];
+    const bool cok = c < a.inner;
+    float * S = a.state + (size_t) a.seg_slot[sg] * a.state_stride + a.state_off + (size_t) (cok ? c : 0) * N;
+    float s[NPL], Ar[NPL];
+#pragma unroll
+    for (int r = 0; r < NPL; r++) {
+        const int k = part + SS_P * r;
+        const bool ok = cok && k < N;
+        s[r] = ok ? S[k] : 0.f;
+        Ar[r] = ok ? a.A[(size_t) c * N + k] : 0.f;
+    }
+    const float Dc = cok ? a.Dk[c] : 0.f;
+    for (int t0 = 0; t0 < n; t0 += SS_TC) {
+        const int nc = min(SS_TC, n - t0);
+        for (int i = threadIdx.x; i < nc * SS_CH; i += blockDim.x) {
+            const int tt = i / SS_CH, cc = i % SS_CH, ch = c0 + cc;
+            const size_t row = (size_t) (s0 + t0 + tt);
+            const bool ok = ch < a.inner;
+            dts[i] = ok ? sk_softplus(a.dtr[row * a.lddt + ch] + a.dt_bias[ch]) : 0.f;
+            us[i]  = ok ? a.u[row * a.ldu + ch] : 0.f;
+            zs[i]  = ok ? a.z[row * a.ldz + ch] : 0.f;
+        }
+        for (int i = threadIdx.x; i < nc * N; i += blockDim.x) {
+            const int tt = i / N, k = i % N;
+            const float * r = a.bc + (size_t) (s0 + t0 + tt) * a.ldbc;
+            Bs[i] = r[k]; Cs[i] = r[N + k];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nc; tt++) {
+            const float dt = dts[tt * SS_CH + cl], u = us[tt * SS_CH + cl], du = dt * u;
+            const float * Bt = Bs + tt * N + part, * Ct = Cs + tt * N + part;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < NPL; r++) {
+                if (part + SS_P * r < N) {
+                    s[r] = fmaf(expf(dt * Ar[r]), s[r], du * Bt[SS_P * r]);
+                    acc = fmaf(s[r], Ct[SS_P * r], acc);
+                }
+            }
+#pragma unroll
+            for (int o = 1; o < SS_P; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (part == 0) ys[tt * SS_CH + cl] = fmaf(Dc, u, acc) * sk_silu(zs[tt * SS_CH + cl]);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc * SS_CH; i += blockDim.x) {
+            const int tt = i / SS_CH, ch = c0 + i % SS_CH;
+            if (ch < a.inner) a.out[(size_t) (s0 + t0 + tt) * a.inner + ch] = ys[i];
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NPL; r++) { const int k = part + SS_P * r; if (cok && k < N) S[k] = s[r]; }
+}
+int pib_ssm_scan(const float * u, int ldu, const float * dtr, int lddt, const float * bc, int ldbc, const float * z, int ldz, const pib_hlayer & L, const pib_hbatch & b,
+                 float * state, size_t state_stride, float * out, cudaStream_t st) {
+    const int N = L.n_state;
+    if (N < 1 || N > SS_P * 64) { pib_set_error("state-space scan: %d states per channel (1 to %d)", N, SS_P * 64); return PIB_ERR_UNSUPP; }
+    ss_args a = { u, ldu, dtr, lddt, bc, ldbc, z, ldz, L.dt_bias, L.ssm_a, L.ssm_d, L.inner, N, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out };
+    dim3 grid((unsigned) b.S, (unsigned) ((L.inner + SS_CH - 1) / SS_CH));
+    const size_t smem = (size_t) (4 * SS_TC * SS_CH + 2 * SS_TC * N) * 4;
+#define SS_GO(NPL) do { if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
+                        pib_launch(ssm_scan_kernel<NPL>, dim3(grid), dim3(SS_CH * SS_P), (size_t) smem, st, a); } while (0)
+    const int per = (N + SS_P - 1) / SS_P;
+    if (per <= 1) SS_GO(1); else if (per <= 2) SS_GO(2); else if (per <= 4) SS_GO(4); else if (per <= 8) SS_GO(8); else if (per <= 16) SS_GO(16); else if (per <= 32) SS_GO(32);
+    else SS_GO(64);
+#undef SS_GO
+    CKL();
+    return PIB_OK;
+}
+
+// ---- two-branch mixer: what follows the projections ---------------------------------------------------------------------------------------
+// proj[t] = [q (H*D) | k (G*D) | head gates (H) | q2 | k2 | v2 | gates2] before any bias.  One warp per query / key head: add the bias, keep
+// the key as the VALUE of the token's cell, rotate the first rot_dims coordinates (i pairs with i + rot_dims / 2), divide by the root mean
+// square over D; queries go to q[t][h], keys to the cell: [keys (G*D) | values (G*D)].  The other threads' share: silu in place on q2 | k2 | v2.
+__global__ void __launch_bounds__(256) dual_prep_kernel(float * __restrict__ proj, int ldp, int H, int G, int D, int rot_dims, const float * __restrict__ bias, float eps,
+                                                        int act_off, int act_n, const int32_t * __restrict__ pos, const int32_t * __restrict__ cell,
+                                                        const float2 * __restrict__ rope, float * __restrict__ q, float * __restrict__ cache, int cache_row) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float sm[];                 // per warp [2][D]
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float * r = proj + (size_t) t * ldp;
+    float * row = cache + (size_t) cell[t] * cache_row;
+    const int half = rot_dims / 2;
+    const float2 * cs = rope + (size_t) pos[t] * half;
+    float * raw = sm + (size_t) warp * 2 * D, * rot = raw + D;
+    for (int hh = warp; hh < H + G; hh += nw) {
+        const float * src = r + (size_t) hh * D;
+        const float * b = bias + (size_t) hh * D;
+        for (int i = lane; i < D; i += 32) {
+            const float v = src[i] + b[i];
+            raw[i] = v;
+            if (hh >= H) row[(size_t) G * D + (size_t) (hh - H) * D + i] = v;
+        }
+        __syncwarp();
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) {
+            float v;
+            if (i < half)          v = raw[i] * cs[i].x - raw[i + half] * cs[i].y;
+            else if (i < rot_dims) v = raw[i] * cs[i - half].x + raw[i - half] * cs[i - half].y;
+            else                   v = raw[i];
+            rot[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / D + eps);
+        float * dst = hh < H ? q + ((size_t) t * H + hh) * D : row + (size_t) (hh - H) * D;
+        for (int i = lane; i < D; i += 32) dst[i] = rot[i] * inv;
+        __syncwarp();
+    }
+    for (int i = threadIdx.x; i < act_n; i += blockDim.x) r[act_off + i] = sk_silu(r[act_off + i]);
+}
+int pib_dual_prep(float * proj, int ldp, const pib_hlayer & L, float eps, const pib_hbatch & b, const float2 * rope, float * q, float * cache, int cache_row, cudaStream_t st) {
+    const int H = L.heads, G = L.kv_heads, D = L.dim, act_off = (H + G) * D + H, act_n = L.heads2 * (2 * L.dim2 + L.vdim2);
+    const size_t smem = (size_t) 8 * 2 * D * 4;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(dual_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    pib_launch(dual_prep_kernel, dim3(b.T), dim3(256), (size_t) smem, st, proj, ldp, H, G, D, L.rot_dims, (const float *) L.proj_bias, eps, act_off, act_n, b.pos, b.cell, rope, q,
+               cache, cache_row);
+    CKL();
+    return PIB_OK;
+}
+
+// out[t] = [ sa * a[t][h][:] * sigmoid(proj[t][ga_off + h])  (H*V)  |  sb * bo[t] / rms(bo[t]) * w * sigmoid(proj[t][gb_off + :])  (H2*V2) ]
+__global__ void __launch_bounds__(256) dual_gate_kernel(const float * __restrict__ a, const float * __restrict__ bo, const float * __restrict__ proj, int ldp, int ga_off, int gb_off,
+                                                        int H, int V, int NB, const float * __restrict__ w, float sa, float sb, float eps, float * __restrict__ out) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    __shared__ float red[32];
+    const size_t t = blockIdx.x;
+    const float * p = proj + t * ldp;
+    float * o = out + t * ((size_t) H * V + NB);
+    for (int i = threadIdx.x; i < H * V; i += blockDim.x) o[i] = sa * a[t * H * V + i] * sk_sigmoid(p[ga_off + i / V]);
+    const float * br = bo + t * NB;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < NB; i += blockDim.x) ss = fmaf(br[i], br[i], ss);
+    const float inv = sb / sqrtf(sk_block_sum(ss, red) / NB + eps);
+    for (int i = threadIdx.x; i < NB; i += blockDim.x) o[(size_t) H * V + i] = br[i] * inv * w[i] * sk_sigmoid(p[gb_off + i]);
+}
+int pib_dual_gate(const float * a, const float * bo, const float * proj, int ldp, int ga_off, int gb_off, const pib_hlayer & L, float eps, int T, float * out, cudaStream_t st) {
+    pib_launch(dual_gate_kernel, dim3(T), dim3(256), (size_t) 0, st, a, bo, proj, ldp, ga_off, gb_off, L.heads, L.vdim, L.heads2 * L.vdim2, (const float *) L.onorm, L.mix_a, L.mix_b,
+               eps, out);
+    CKL();
+    return PIB_OK;
+}

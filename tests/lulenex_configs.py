@@ -1,0 +1,89 @@
+"""Small Lulenex configurations for the tests (sizes chosen to differ from each other: heads, key / value heads, dims, chunks, rotated
+dimensions, states, taps, walks)."""
+import math
+
+
+def ssm(inner, state, dt_rank, conv):
+    return {"inner": inner, "state": state, "dt_rank": dt_rank, "conv": conv}
+
+
+def softmax_branch(heads, kv_heads, dim, chunk, rot_dims, base=10000.0, scale=None):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": chunk}, "rot": {"base": base, "dims": rot_dims},
+            "scale": scale if scale is not None else 1.0 / math.sqrt(dim)}
+
+
+def linear_branch(heads, dim, vdim, decay):
+    assert len(decay) == heads
+    return {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}
+
+
+def two(left, right, a=0.7, b=1.2):
+    return {"left": left, "right": right, "left_scale": a, "right_scale": b}
+
+
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def model(width, vocab, layers, loop=None, eps=1e-6):
+    cfg = {"architecture": "Lulenex", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": [{"type": t, "mixer": mx, "mlp": ml} for t, mx, ml in layers]}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def mixed_small():
+    """both mixers, a walked run in the middle that ends with the state-space layer, a layer without feed-forward"""
+    return model(80, 190, [("parallel", two(softmax_branch(4, 2, 12, 7, 8), linear_branch(3, 10, 14, [0.5, 0.9, 0.97])), dense(100)),
+                           ("parallel", two(softmax_branch(2, 2, 20, 11, 20, base=500.0, scale=0.4), linear_branch(1, 24, 8, [0.8]), a=1.3, b=0.5), None),
+                           ("mamba1", ssm(96, 6, 5, 3), dense(72)),
+                           ("mamba1", ssm(40, 17, 9, 2), None),
+                           ("parallel", two(softmax_branch(6, 3, 8, 5, 4), linear_branch(2, 12, 12, [0.3, 0.99])), dense(64))], loop=(1, 3, 2))
+
+
+def ssm_only():
+    return model(48, 100, [("mamba1", ssm(72, 8, 4, 4), None), ("mamba1", ssm(50, 33, 7, 3), dense(40))])
+
+
+def softmax_mostly():
+    """the linear branch nearly silent: what the logits show is the chunked attention (rotation, unit norms, sink, values = keys, gates)"""
+    return model(64, 120, [("parallel", two(softmax_branch(4, 2, 16, 9, 10, scale=0.6), linear_branch(1, 4, 4, [0.5]), a=1.0, b=0.01), None),
+                           ("parallel", two(softmax_branch(3, 1, 12, 9, 12, base=77.0), linear_branch(1, 4, 4, [0.5]), a=1.0, b=0.01), None)])
+
+
+def linear_mostly():
+    return model(56, 90, [("parallel", two(softmax_branch(1, 1, 8, 4, 2), linear_branch(3, 20, 12, [0.6, 0.95, 0.999]), a=0.01, b=1.0), None),
+                          ("parallel", two(softmax_branch(1, 1, 8, 4, 2), linear_branch(2, 6, 30, [0.2, 1.0]), a=0.01, b=1.0), dense(30))])
+
+
+def walks():
+    """the whole model is one walked run, three walks; then a run of one layer walked twice in front of others"""
+    return model(40, 70, [("mamba1", ssm(48, 4, 3, 2), dense(32)), ("parallel", two(softmax_branch(2, 1, 8, 6, 8), linear_branch(2, 8, 8, [0.7, 0.9])), dense(48))], loop=(0, 2, 3))
+
+
+def one_layer_walk():
+    return model(40, 70, [("parallel", two(softmax_branch(2, 1, 8, 6, 8), linear_branch(2, 8, 8, [0.7, 0.9])), dense(48)),
+                          ("mamba1", ssm(48, 4, 3, 2), None), ("mamba1", ssm(24, 5, 2, 4), dense(16))], loop=(1, 2, 2))
+
+
+def ones():
+    """values that happen to be 1 or equal: one head, one key head, one state, rank 1, one tap, chunks of 1, one walk, scales 1"""
+    return model(32, 40, [("parallel", two(softmax_branch(1, 1, 16, 1, 16, scale=1.0), linear_branch(1, 16, 16, [1.0]), a=1.0, b=1.0), dense(32)),
+                          ("mamba1", ssm(32, 1, 1, 1), dense(32)),
+                          ("parallel", two(softmax_branch(1, 1, 16, 4096, 0), linear_branch(1, 16, 16, [0.5]), a=1.0, b=1.0), None)], loop=(0, 3, 1))
+
+
+def far_keys():
+    """long chunks and a peaky softmax: single keys hundreds of tokens back carry the output"""
+    return model(64, 300, [("parallel", two(softmax_branch(2, 1, 24, 260, 12, scale=2.0), linear_branch(1, 8, 8, [0.9]), a=1.0, b=0.05), None),
+                           ("parallel", two(softmax_branch(4, 4, 8, 193, 8, scale=3.0), linear_branch(1, 8, 8, [0.9]), a=1.0, b=0.05), None)])
+
+
+def wide_heads():
+    """head sizes that are multiples of 8: long portions take the tensor-core (matmul) form of the attention in served mode"""
+    return model(64, 160, [("parallel", two(softmax_branch(4, 2, 32, 150, 16), linear_branch(2, 16, 16, [0.8, 0.95])), dense(96)),
+                           ("mamba1", ssm(128, 16, 4, 4), None),
+                           ("parallel", two(softmax_branch(2, 2, 16, 37, 16), linear_branch(2, 16, 24, [0.9, 0.99])), None)], loop=(0, 2, 2))
+
+
+CONFIGS = {f.__name__: f for f in (mixed_small, ssm_only, softmax_mostly, linear_mostly, walks, one_layer_walk, ones, far_keys, wide_heads)}
