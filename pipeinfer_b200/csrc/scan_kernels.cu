@@ -152,13 +152,13 @@ int pib_xielu(float * z, int T, int F, float p, float q, cudaStream_t st) {
 }
 
 // ---- selective state-space scan --------------------------------------------------------------------------------------------------------
-// grid (segment, tile of SS_CH channels), SS_CH * SS_P threads: the SS_P lanes of a channel keep states part, part + SS_P, ... in
-// registers.  A chunk of SS_TC tokens is staged in shared memory (dt with its bias and softplus applied once per channel and token),
-// walked token by token, and its outputs leave in whole rows.  The states are read from the slot at the segment's start and left there
-// at its end.
-#define SS_CH 32
-#define SS_P  4
-#define SS_TC 16
+// grid (segment, tile of SS_THREADS / P channels), SS_THREADS threads: the P lanes of a channel keep states part, part + P, ... in
+// registers (P = 16 for 16 states and more: one state per lane at 16, so that a layer of a few thousand channels fills the machine with
+// warps).  A chunk of SS_TC tokens is staged in shared memory (dt with its bias and softplus applied once per channel and token),
+// walked token by token, and its outputs leave in whole rows, gated by silu(z) on the way out.  The states are read from the slot at
+// the segment's start and left there at its end.
+#define SS_THREADS 128
+#define SS_TC      16
 struct ss_args {
     const float * u; int ldu;                // after convolution and silu
     const float * dtr; int lddt;             // W_dt (.) before bias and softplus
@@ -170,20 +170,21 @@ struct ss_args {
     float * state; size_t state_stride, state_off;
     float * out;                             // [T][inner]
 };
-template <int NPL>
-__global__ void __launch_bounds__(SS_CH * SS_P) ssm_scan_kernel(ss_args a) {
+template <int P, int NPL>
+__global__ void __launch_bounds__(SS_THREADS) ssm_scan_kernel(ss_args a) {
     pib_pdl_wait();
     pib_pdl_trigger();
+    constexpr int CH = SS_THREADS / P, TB = NPL <= 2 ? 4 : NPL <= 8 ? 2 : 1;
     extern __shared__ float sm[];
-    const int N = a.N, sg = blockIdx.x, c0 = blockIdx.y * SS_CH, cl = threadIdx.x / SS_P, part = threadIdx.x % SS_P, c = c0 + cl;
-    float * dts = sm, * us = dts + SS_TC * SS_CH, * zs = us + SS_TC * SS_CH, * ys = zs + SS_TC * SS_CH, * Bs = ys + SS_TC * SS_CH, * Cs = Bs + SS_TC * N;
+    const int N = a.N, sg = blockIdx.x, c0 = blockIdx.y * CH, cl = threadIdx.x / P, part = threadIdx.x % P, c = c0 + cl;
+    float * dts = sm, * us = dts + SS_TC * CH, * zs = us + SS_TC * CH, * ys = zs + SS_TC * CH, * Bs = ys + SS_TC * CH, * Cs = Bs + SS_TC * N;
     const int s0 = a.seg_start[sg], n = a.seg_len[sg];
     const bool cok = c < a.inner;
     float * S = a.state + (size_t) a.seg_slot[sg] * a.state_stride + a.state_off + (size_t) (cok ? c : 0) * N;
     float s[NPL], Ar[NPL];
 #pragma unroll
     for (int r = 0; r < NPL; r++) {
-        const int k = part + SS_P * r;
+        const int k = part + P * r;
         const bool ok = cok && k < N;
         s[r] = ok ? S[k] : 0.f;
         Ar[r] = ok ? a.A[(size_t) c * N + k] : 0.f;
@@ -191,8 +192,8 @@ __global__ void __launch_bounds__(SS_CH * SS_P) ssm_scan_kernel(ss_args a) {
     const float Dc = cok ? a.Dk[c] : 0.f;
     for (int t0 = 0; t0 < n; t0 += SS_TC) {
         const int nc = min(SS_TC, n - t0);
-        for (int i = threadIdx.x; i < nc * SS_CH; i += blockDim.x) {
-            const int tt = i / SS_CH, cc = i % SS_CH, ch = c0 + cc;
+        for (int i = threadIdx.x; i < nc * CH; i += blockDim.x) {
+            const int tt = i / CH, cc = i % CH, ch = c0 + cc;
             const size_t row = (size_t) (s0 + t0 + tt);
             const bool ok = ch < a.inner;
             dts[i] = ok ? sk_softplus(a.dtr[row * a.lddt + ch] + a.dt_bias[ch]) : 0.f;
@@ -205,42 +206,73 @@ __global__ void __launch_bounds__(SS_CH * SS_P) ssm_scan_kernel(ss_args a) {
             Bs[i] = r[k]; Cs[i] = r[N + k];
         }
         __syncthreads();
-        for (int tt = 0; tt < nc; tt++) {
-            const float dt = dts[tt * SS_CH + cl], u = us[tt * SS_CH + cl], du = dt * u;
-            const float * Bt = Bs + tt * N + part, * Ct = Cs + tt * N + part;
-            float acc = 0.f;
+        // TB tokens at a time: their decays exp(dt A) and inputs dt u B do not depend on the states, so they are formed side by side; only
+        // the fused multiply-adds on the states run one after the other
+        for (int tb = 0; tb < nc; tb += TB) {
+            float dA[TB][NPL], dB[TB][NPL], uu[TB];
 #pragma unroll
-            for (int r = 0; r < NPL; r++) {
-                if (part + SS_P * r < N) {
-                    s[r] = fmaf(expf(dt * Ar[r]), s[r], du * Bt[SS_P * r]);
-                    acc = fmaf(s[r], Ct[SS_P * r], acc);
+            for (int j = 0; j < TB; j++) {
+                const int tt = min(tb + j, nc - 1);
+                const float dt = dts[tt * CH + cl], u = us[tt * CH + cl], du = dt * u;
+                const float * Bt = Bs + tt * N + part;
+                uu[j] = u;
+#pragma unroll
+                for (int r = 0; r < NPL; r++) {
+                    const bool ok = part + P * r < N;
+                    dA[j][r] = expf(dt * Ar[r]);
+                    dB[j][r] = ok ? du * Bt[P * r] : 0.f;
+                }
+            }
+            float acc[TB];
+#pragma unroll
+            for (int j = 0; j < TB; j++) {
+                const int tt = min(tb + j, nc - 1);
+                const float * Ct = Cs + tt * N + part;
+                acc[j] = 0.f;
+                if (tb + j < nc) {
+#pragma unroll
+                    for (int r = 0; r < NPL; r++) {
+                        s[r] = fmaf(dA[j][r], s[r], dB[j][r]);
+                        if (part + P * r < N) acc[j] = fmaf(s[r], Ct[P * r], acc[j]);
+                    }
                 }
             }
 #pragma unroll
-            for (int o = 1; o < SS_P; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (part == 0) ys[tt * SS_CH + cl] = fmaf(Dc, u, acc) * sk_silu(zs[tt * SS_CH + cl]);
+            for (int o = 1; o < P; o <<= 1)
+#pragma unroll
+                for (int j = 0; j < TB; j++) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+            if (part < TB && tb + part < nc) {                 // lane j of the channel stores token j's sum
+                float v = acc[0];
+#pragma unroll
+                for (int j = 1; j < TB; j++) if (part == j) v = acc[j];
+                float uj = uu[0];
+#pragma unroll
+                for (int j = 1; j < TB; j++) if (part == j) uj = uu[j];
+                ys[(tb + part) * CH + cl] = fmaf(Dc, uj, v);
+            }
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < nc * SS_CH; i += blockDim.x) {
-            const int tt = i / SS_CH, ch = c0 + i % SS_CH;
-            if (ch < a.inner) a.out[(size_t) (s0 + t0 + tt) * a.inner + ch] = ys[i];
+        for (int i = threadIdx.x; i < nc * CH; i += blockDim.x) {
+            const int tt = i / CH, ch = c0 + i % CH;
+            if (ch < a.inner) a.out[(size_t) (s0 + t0 + tt) * a.inner + ch] = ys[i] * sk_silu(zs[i]);
         }
     }
 #pragma unroll
-    for (int r = 0; r < NPL; r++) { const int k = part + SS_P * r; if (cok && k < N) S[k] = s[r]; }
+    for (int r = 0; r < NPL; r++) { const int k = part + P * r; if (cok && k < N) S[k] = s[r]; }
 }
 int pib_ssm_scan(const float * u, int ldu, const float * dtr, int lddt, const float * bc, int ldbc, const float * z, int ldz, const pib_hlayer & L, const pib_hbatch & b,
                  float * state, size_t state_stride, float * out, cudaStream_t st) {
     const int N = L.n_state;
-    if (N < 1 || N > SS_P * 64) { pib_set_error("state-space scan: %d states per channel (1 to %d)", N, SS_P * 64); return PIB_ERR_UNSUPP; }
+    if (N < 1 || N > 256) { pib_set_error("state-space scan: %d states per channel (1 to 256)", N); return PIB_ERR_UNSUPP; }
     ss_args a = { u, ldu, dtr, lddt, bc, ldbc, z, ldz, L.dt_bias, L.ssm_a, L.ssm_d, L.inner, N, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out };
-    dim3 grid((unsigned) b.S, (unsigned) ((L.inner + SS_CH - 1) / SS_CH));
-    const size_t smem = (size_t) (4 * SS_TC * SS_CH + 2 * SS_TC * N) * 4;
-#define SS_GO(NPL) do { if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
-                        pib_launch(ssm_scan_kernel<NPL>, dim3(grid), dim3(SS_CH * SS_P), (size_t) smem, st, a); } while (0)
-    const int per = (N + SS_P - 1) / SS_P;
-    if (per <= 1) SS_GO(1); else if (per <= 2) SS_GO(2); else if (per <= 4) SS_GO(4); else if (per <= 8) SS_GO(8); else if (per <= 16) SS_GO(16); else if (per <= 32) SS_GO(32);
-    else SS_GO(64);
+    const int P = N >= 16 ? 16 : N >= 8 ? 8 : 4, CH = SS_THREADS / P, per = (N + P - 1) / P;
+    dim3 grid((unsigned) b.S, (unsigned) ((L.inner + CH - 1) / CH));
+    const size_t smem = (size_t) (4 * SS_TC * CH + 2 * SS_TC * N) * 4;
+#define SS_GO(P, NPL) do { if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<P, NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
+                           pib_launch(ssm_scan_kernel<P, NPL>, dim3(grid), dim3(SS_THREADS), (size_t) smem, st, a); } while (0)
+    if (P == 4)      { if (per <= 1) SS_GO(4, 1); else SS_GO(4, 2); }
+    else if (P == 8) { if (per <= 1) SS_GO(8, 1); else SS_GO(8, 2); }
+    else if (per <= 1) SS_GO(16, 1); else if (per <= 2) SS_GO(16, 2); else if (per <= 4) SS_GO(16, 4); else if (per <= 8) SS_GO(16, 8); else SS_GO(16, 16);
 #undef SS_GO
     CKL();
     return PIB_OK;

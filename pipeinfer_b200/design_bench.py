@@ -1,8 +1,8 @@
-"""`bench.py --design rapisun | fabivik`: prefill and decode throughput of a layer-list design at sizes that resemble a real model's
-layers (random weights drawn in the loader from a seed), beside the closest existing model of the library at equal width / depth /
+"""`bench.py --design rapisun | fabivik | lulenex`: prefill and decode throughput of a layer-list design at sizes that resemble a real
+model's layers (random weights drawn in the loader from a seed), beside the closest existing model of the library at equal width / depth /
 vocabulary -- for Rapisun the llama architecture in Q4_K (prompts on its tcgen05 GEMM, decoding on its tensor-core GEMVs), for Fabivik
-the Rapisun design (the other layer-list model: same runtime, same dense matmuls) -- plus the share and the roofline fraction of every
-kind of launch.  Everything goes through llama_decode on host batches; times are medians of CUDA-side
+the Rapisun design (the other layer-list model: same runtime, same dense matmuls), for Lulenex the Fabivik design (attention over cached
+key / value heads and recurrences on the same kernels) -- plus the share and the roofline fraction of every kind of launch.  Everything goes through llama_decode on host batches; times are medians of CUDA-side
 work as seen by the caller (llama_decode returns after the run's event), the per-kind numbers come from CUDA events around each
 launch (llama_pib_profile_layer).  One JSON line on stdout."""
 import ctypes as C
@@ -52,6 +52,24 @@ def fabivik_config(width, vocab, blocks, heads, window, experts, top, ff_e, ff_s
                    {"type": "attention", "mixer": att, "mlp": moe}, {"type": "wkv", "mixer": wkv, "mlp": moe}]
     return {"architecture": "Fabivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0}, "logit_scale": 0.5, "layers": layers}
 
+
+def lulenex_config(width, vocab, blocks, heads, window, ff, **_):
+    """4 * blocks layer runs: [state-space scan, two-branch, two-branch, two-branch] per block without the last layer, the second layer walked twice;
+    every layer with a dense feed-forward"""
+    ssm = {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}
+    two = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "mask": {"size": window}, "rot": {"base": 500000.0, "dims": 64},
+                    "scale": 1.0 / math.sqrt(128)},
+           "right": {"heads": max(1, heads // 2), "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, heads // 2)) for h in range(max(1, heads // 2))]},
+           "left_scale": 0.7, "right_scale": 0.9}
+    dense = {"kind": "dense", "ff": ff}
+    layers = ([{"type": "mamba1", "mixer": ssm, "mlp": dense}] + [{"type": "parallel", "mixer": two, "mlp": dense}] * 3) * blocks
+    return {"architecture": "Lulenex", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": layers[:-1], "loop": {"start": 1, "stop": 2, "times": 2}}
+
+
+# design -> (its name, its configuration, the comparator's key)
+DESIGNS = {"rapisun": ("Rapisun", design_config, "llama_q4k"), "fabivik": ("Fabivik", fabivik_config, "rapisun"), "lulenex": ("Lulenex", lulenex_config, "fabivik")}
+COMPARATORS = {"llama_q4k": "llama architecture, Q4_K", "rapisun": "Rapisun (layer-list design of this library), same width / depth / vocabulary / experts",
+               "fabivik": "Fabivik (layer-list design of this library), same width / layer runs / vocabulary"}
 
 SIZES = {
     # name: (design arguments, llama comparator (n_layer, n_embd, n_head, n_head_kv, n_ff, n_vocab))
@@ -202,18 +220,18 @@ def run(args):
         scratch.zero_()
         torch.cuda.synchronize()
 
-    fab = args.design == "fabivik"
-    out = {"design": "Fabivik" if fab else "Rapisun", "metric": "prefill / decode tokens per second, one GPU",
-           "dtype": "bf16 operands, fp32 accumulation" + ("" if fab else " (comparator: Q4_K x Q8_K)"),
-           "comparator": "Rapisun (layer-list design of this library), same width / depth / vocabulary / experts" if fab else "llama architecture, Q4_K",
+    key = args.design
+    title, make_config, cmp_key = DESIGNS[key]
+    out = {"design": title, "metric": "prefill / decode tokens per second, one GPU",
+           "dtype": "bf16 operands, fp32 accumulation" + (" (comparator: Q4_K x Q8_K)" if cmp_key == "llama_q4k" else ""),
+           "comparator": COMPARATORS[cmp_key],
            "data": "synthetic (random weights from a seed)", "peaks": peaks, "l2_policy": "256 MB written between timed calls", "sizes": {}}
     lens = [int(x) for x in args.design_prompt.split(",")]
     for name in args.design_size.split(","):
         dargs, cmp_shape = SIZES[name]
-        cfg = fabivik_config(**dargs) if fab else design_config(**dargs)
+        cfg = make_config(**dargs)
         vocab = dargs["vocab"]
         n_ctx = max(lens) + 512
-        key = "fabivik" if fab else "rapisun"
         t0 = time.time()
         ours = llama.Context(config=json.dumps(cfg), seed=1, n_ctx=4 * 320 + n_ctx, max_seq=8, state_slots=4)
         entry = {"config": dargs, "layers": len(cfg["layers"]), "load_s": round(time.time() - t0, 1)}
@@ -221,11 +239,11 @@ def run(args):
         entry[key + "_prefill_kinds"] = _profile_design(ours, lib, max(lens), vocab, False, peaks)
         entry[key + "_decode_kinds"] = _profile_design(ours, lib, 256, vocab, True, peaks)
         ours.close()
-        if fab:
-            cmpc = llama.Context(config=json.dumps(design_config(**dargs)), seed=1, n_ctx=4 * 320 + n_ctx, max_seq=8, state_slots=4)
-            entry["rapisun"] = _measure(cmpc, lib, lens, 32, [1, 4], vocab, flush, args.warmup, args.steps)
-            entry["rapisun_prefill_kinds"] = _profile_design(cmpc, lib, max(lens), vocab, False, peaks)
-            entry["rapisun_decode_kinds"] = _profile_design(cmpc, lib, 256, vocab, True, peaks)
+        if cmp_key != "llama_q4k":
+            cmpc = llama.Context(config=json.dumps(DESIGNS[cmp_key][1](**dargs)), seed=1, n_ctx=4 * 320 + n_ctx, max_seq=8, state_slots=4)
+            entry[cmp_key] = _measure(cmpc, lib, lens, 32, [1, 4], vocab, flush, args.warmup, args.steps)
+            entry[cmp_key + "_prefill_kinds"] = _profile_design(cmpc, lib, max(lens), vocab, False, peaks)
+            entry[cmp_key + "_decode_kinds"] = _profile_design(cmpc, lib, 256, vocab, True, peaks)
             cmpc.close()
         else:
             L, E, H, HKV, FF, V = cmp_shape
