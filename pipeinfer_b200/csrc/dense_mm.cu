@@ -30,6 +30,7 @@ struct mm_dev {
     float * Y; int64_t ldy, yz;
     int M, N, K;
     const int32_t * zrange;
+    float e0, e1;
 };
 
 template <typename WT, bool ROUND, int EPI>
@@ -99,9 +100,7 @@ __global__ void __launch_bounds__(256) mm_tile_kernel(mm_dev a) {
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
             if (n >= a.N) continue;
-            float v = acc[i][j];
-            if (EPI == PIB_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
-            Y[(size_t) m * a.ldy + n] = v;
+            Y[(size_t) m * a.ldy + n] = pib_epilogue<EPI, ROUND>(acc[i][j], a.e0, a.e1);
         }
     }
 }
@@ -168,10 +167,7 @@ __device__ __forceinline__ void mv_rows_body(const mm_dev & a, bool xvec, int z,
 #pragma unroll
     for (int b = 0; b < B; b++) {
         float v = warp_sum(acc[b]);
-        if (lane == 0 && row0 + b < row1) {
-            if (EPI == PIB_EPI_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
-            Y[(size_t) (row0 + b) * a.ldy + n] = v;
-        }
+        if (lane == 0 && row0 + b < row1) Y[(size_t) (row0 + b) * a.ldy + n] = pib_epilogue<EPI, ROUND>(v, a.e0, a.e1);
     }
 }
 
@@ -256,7 +252,7 @@ int pib_dense_mm(const pib_mm & a, cudaStream_t st) {
         if (rc != PIB_ERR_UNSUPP) return rc;
     }
     if (a.x_bf16) { pib_set_error("dense matmul: bfloat16 activations need the tensor-core path (more than 16 rows, strides multiples of 8)"); return PIB_ERR_UNSUPP; }
-    mm_dev d = { a.W, a.ldw, a.wz, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.Y, a.ldy, a.yz, a.M, a.N, a.K, a.zrange };
+    mm_dev d = { a.W, a.ldw, a.wz, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.Y, a.ldy, a.yz, a.M, a.N, a.K, a.zrange, a.e0, a.e1 };
     if (a.wtype == PIB_TYPE_F32 && a.exact && a.N <= 32 && a.M > MV_MAXB && a.Z == 1 && !a.xrows && !a.zrange && a.epi == PIB_EPI_NONE) {
         dim3 grid((unsigned) ((a.M + 7) / 8));
         if (a.N <= 8)       pib_launch(mm_few_cols_kernel<8>, dim3(grid), dim3(256), (size_t) 0, st, d);
@@ -265,7 +261,8 @@ int pib_dense_mm(const pib_mm & a, cudaStream_t st) {
         PIB_CHECK(cudaGetLastError());
         return PIB_OK;
     }
-#define MM_GO(WT, ROUND) (a.epi == PIB_EPI_RELU2 ? launch_mm<WT, ROUND, PIB_EPI_RELU2>(a, d, st) : launch_mm<WT, ROUND, PIB_EPI_NONE>(a, d, st))
+#define MM_GO(WT, ROUND) (a.epi == PIB_EPI_RELU2 ? launch_mm<WT, ROUND, PIB_EPI_RELU2>(a, d, st) : a.epi == PIB_EPI_XIELU ? launch_mm<WT, ROUND, PIB_EPI_XIELU>(a, d, st) : \
+                                                    launch_mm<WT, ROUND, PIB_EPI_NONE>(a, d, st))
     if (a.wtype == PIB_TYPE_BF16) return MM_GO(__nv_bfloat16, true);
     if (a.wtype == PIB_TYPE_F32) return a.exact ? MM_GO(float, false) : MM_GO(float, true);
 #undef MM_GO

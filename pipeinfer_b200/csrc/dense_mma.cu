@@ -89,7 +89,7 @@ template <int NB> struct dt_cfg {
 template <int NB, int EPI>
 __global__ void __launch_bounds__(DT_THREADS)
 dense_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, int M, int N, int K, const int32_t * __restrict__ zrange,
-                int x_has_z, float * __restrict__ Y, int64_t ldy, int64_t yz, int * __restrict__ err) {
+                int x_has_z, float * __restrict__ Y, int64_t ldy, int64_t yz, int * __restrict__ err, float e0, float e1) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int z = blockIdx.z;
@@ -175,9 +175,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
                     for (int j = 0; j < 32; j++) {
                         const int m = m0 + c0 + j;
                         if (m < row1) {
-                            float f = __uint_as_float(v[j]);
-                            if (EPI == PIB_EPI_RELU2) { f = fmaxf(f, 0.f); f = f * f; }
-                            Yz[(size_t) m * ldy + orow] = f;
+                            Yz[(size_t) m * ldy + orow] = pib_epilogue<EPI, true>(__uint_as_float(v[j]), e0, e1);
                         }
                     }
                 }
@@ -250,11 +248,13 @@ static int dt_launch(const pib_mm & a, const CUtensorMap & wmap, const CUtensorM
     if (!configured) {
         PIB_CHECK(cudaFuncSetAttribute(dense_tc_kernel<NB, PIB_EPI_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
         PIB_CHECK(cudaFuncSetAttribute(dense_tc_kernel<NB, PIB_EPI_RELU2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
+        PIB_CHECK(cudaFuncSetAttribute(dense_tc_kernel<NB, PIB_EPI_XIELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
         configured = true;
     }
     dim3 grid((unsigned) ((a.N + DT_BM - 1) / DT_BM), (unsigned) ((a.M + NB - 1) / NB), (unsigned) a.Z);
-    if (a.epi == PIB_EPI_RELU2) pib_launch(dense_tc_kernel<NB, PIB_EPI_RELU2>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err);
-    else                        pib_launch(dense_tc_kernel<NB, PIB_EPI_NONE>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err);
+    if (a.epi == PIB_EPI_RELU2)      pib_launch(dense_tc_kernel<NB, PIB_EPI_RELU2>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err, a.e0, a.e1);
+    else if (a.epi == PIB_EPI_XIELU) pib_launch(dense_tc_kernel<NB, PIB_EPI_XIELU>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err, a.e0, a.e1);
+    else                             pib_launch(dense_tc_kernel<NB, PIB_EPI_NONE>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err, a.e0, a.e1);
     PIB_CHECK(cudaGetLastError());
     return PIB_OK;
 }

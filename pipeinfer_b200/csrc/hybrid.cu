@@ -52,12 +52,12 @@ static const char * const HK_NAMES[] = { "cellmap", "embed_ln", "canon_conv", "m
                                          "embed_scale", "rms_norm_pair", "mm_qkv", "qkv_conv", "attn_prep", "kv_attention", "kv_attention_mm", "token_shift", "mm_rkvg", "mm_decay",
                                          "decay_act", "wkv_scan", "delta_prep", "delta_scan", "gated_head_norm", "glu_clamp", "parallel_sum",
                                          "embed_pair", "prenorm_shift", "loop_concat", "mm_loop_in", "mm_ssm_in", "ssm_conv", "mm_ssm_x", "mm_ssm_dt", "ssm_scan", "mm_ssm_o",
-                                         "mm_dual_proj", "dual_prep", "decay_scan", "dual_gate", "mm_dual_o", "xielu" };
+                                         "mm_dual_proj", "dual_prep", "decay_scan", "dual_gate", "mm_dual_o" };
 enum { HK_CELLMAP, HK_EMBED, HK_CANON, HK_DQKV, HK_LPREP, HK_UQ, HK_ABSORB, HK_LATTN, HK_UV, HK_AO, HK_QFV, HK_GATES, HK_SCAN, HK_HO, HK_LNRES, HK_UP, HK_POLY, HK_DOWN,
        HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_LATTN_MM,
        HK_EMBSCALE, HK_NORM2, HK_QKV, HK_QKVCONV, HK_APREP, HK_KVATTN, HK_KVATTN_MM, HK_SHIFT, HK_RKVG, HK_DECAY, HK_DECAYACT, HK_WKVSCAN, HK_DPREP, HK_DSCAN, HK_GHNORM, HK_GLU,
        HK_PSUM, HK_EMBPAIR, HK_PRENORM, HK_CONCAT, HK_LOOPIN, HK_SSMIN, HK_SSMCONV, HK_SSMX, HK_SSMDT, HK_SSMSCAN, HK_SSMO, HK_DUALPROJ, HK_DUALPREP, HK_DECAYSCAN, HK_DUALGATE,
-       HK_DUALO, HK_XIELU, HK_COUNT };
+       HK_DUALO, HK_COUNT };
 const char * pib_hybrid_kind_name(int k) { return k >= 0 && k < HK_COUNT ? HK_NAMES[k] : "?"; }
 
 // fetch and clear the records; returns the count (the stream is synchronised)
@@ -231,9 +231,10 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         for (int i = 0; i < T; i++) n += mask == PIB_MASK_CHUNK ? B_pos_host[i] % window + 1 : std::min(B_pos_host[i] + 1, window);
         return n;
     };
-    auto mm = [&](const pib_weight * w, const float * X, int ldx, float * Y, int ldy, int epi) {
+    auto mm = [&](const pib_weight * w, const float * X, int ldx, float * Y, int ldy, int epi, float e0 = 0.f, float e1 = 0.f) {
         pib_mm a;
         a.W = w->base; a.wtype = w->type; a.ldw = w->K; a.X = X; a.ldx = ldx; a.Y = Y; a.ldy = ldy; a.M = T; a.N = (int) w->N; a.K = (int) w->K; a.epi = epi;
+        a.e0 = e0; a.e1 = e1;
         a.exact = exact || w->type == PIB_TYPE_F32;
         return pib_dense_mm(a, st);
     };
@@ -482,8 +483,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             pend_y = x->y; pend_b = L.o_bias;
             if (L.mlp == PIB_MLP_XIELU) {
                 if ((rc = prenorm(L.g2, nullptr, 0, true)) != PIB_OK) return rc;
-                RC(HK_UP, mmfl(L.up), mmby(L.up), mm(L.up, x->h, W, x->proj, L.ff, PIB_EPI_NONE));
-                RC(HK_XIELU, 0, 8.0 * Td * L.ff, pib_xielu(x->proj, T, L.ff, L.act[0], L.act[1], st));
+                RC(HK_UP, mmfl(L.up), mmby(L.up), mm(L.up, x->h, W, x->proj, L.ff, PIB_EPI_XIELU, L.act[2], L.act[3]));      // the activation rides on the matmul's way out
                 RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
                 pend_y = x->y; pend_b = nullptr;
             } else if (L.mlp != PIB_MLP_NONE) { pib_set_error("decode: feed-forward %d in a pre-norm layer", L.mlp); return PIB_ERR_UNSUPP; }

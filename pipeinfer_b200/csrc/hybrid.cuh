@@ -29,7 +29,8 @@ enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2, PIB_MIXER_SWA = 3, PIB_MIXER_W
 enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2, PIB_MLP_XIELU = 3 };
 // which earlier positions j a token at p may read: the last `window` ones (p - window < j <= p), or those of its own chunk (j / window == p / window)
 enum { PIB_MASK_WINDOW = 0, PIB_MASK_CHUNK = 1 };
-enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1 };
+// what a matmul does to an output on its way out: nothing; max(y, 0)^2; xIELU (y > 0: e0 y^2 + y/2, else e1 (exp(y) - 1 - y) + y/2)
+enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1, PIB_EPI_XIELU = 2 };
 // layer forms: x += LN(mixer(conv(x))), x += LN(ff(x))   |   x += mixer(N1(x)) + ff(N2(x)), N = RMS norm with weight (1 + w)
 //              x += mixer(shift(N(x))), x += ff(N(x)), N = RMS norm times one number, shift(h)_t = h_t + (h_{t-1} - h_t) * mu
 enum { PIB_FORM_POSTNORM = 0, PIB_FORM_PARALLEL = 1, PIB_FORM_PRENORM = 2 };
@@ -153,9 +154,21 @@ struct pib_mm {
     int             M = 0, N = 0, K = 0, Z = 1;
     const int32_t * zrange = nullptr;                    // device [Z + 1]: z owns rows [zrange[z], zrange[z + 1]); null: all M rows, every z
     int             epi = PIB_EPI_NONE;
+    float           e0 = 0.f, e1 = 0.f;                  // the epilogue's constants (xIELU: softplus(p), 1/2 + softplus(q))
     int             exact = 0;                           // 1: operands stay fp32 (no bfloat16 rounding of X); W must be float32
     int             x_bf16 = 0;                          // 1: X already holds bfloat16 rows (ldx in elements, a multiple of 8): tensor-core path only, no staging copy
 };
+#ifdef __CUDACC__
+// FAST (served mode, where the result is rounded to bfloat16 as the next matmul's operand): the exponential through ex2.approx, no branch
+template <int EPI, bool FAST> __device__ __forceinline__ float pib_epilogue(float v, float e0, float e1) {
+    if (EPI == PIB_EPI_RELU2) { v = fmaxf(v, 0.f); return v * v; }
+    if (EPI == PIB_EPI_XIELU) {
+        if (FAST) { const float n = fminf(v, 0.f), neg = fmaf(e1, (__expf(n) - 1.0f) - n, 0.5f * v), pos = fmaf(e0 * v, v, 0.5f * v); return v > 0.f ? pos : neg; }
+        return v > 0.f ? fmaf(e0 * v, v, 0.5f * v) : fmaf(e1, expm1f(v) - v, 0.5f * v);
+    }
+    return v;
+}
+#endif
 int pib_dense_mm(const pib_mm & a, cudaStream_t st);
 int pib_dense_mm_check(cudaStream_t st, int enqueue);   // dense_mma.cu: the error word of the bounded waits (1: copy it in stream order, 0: read the copy)
 pib_weight * pib_dense_upload(int type, const void * host, int64_t N, int64_t K);   // type: PIB_TYPE_BF16 / PIB_TYPE_F32, row-major [N][K]
@@ -210,7 +223,6 @@ int pib_prenorm_shift(const float * xin, const float * y, const float * bias, fl
                       size_t state_stride, size_t shift_off, int W, float * h, cudaStream_t st);
 int pib_embed_pair(const pib_weight * embd, const int32_t * tok, int T, int W, float * x, float * cat, cudaStream_t st);
 int pib_concat_stream(const float * xin, const float * y, const float * bias, int T, int W, float * cat, cudaStream_t st);
-int pib_xielu(float * z, int T, int F, float p, float q, cudaStream_t st);
 int pib_ssm_scan(const float * u, int ldu, const float * dtr, int lddt, const float * bc, int ldbc, const float * z, int ldz, const pib_hlayer & L, const pib_hbatch & b,
                  float * state, size_t state_stride, float * out, cudaStream_t st);
 int pib_dual_prep(float * proj, int ldp, const pib_hlayer & L, float eps, const pib_hbatch & b, const float2 * rope, float * q, float * cache, int cache_row, cudaStream_t st);

@@ -664,6 +664,8 @@ static pib_model * build_lulenex(const Json & cfg, TensorSource & src, int dtype
             MAT(L.down, pm + "down", W, L.ff);
             GET(pm + "act", 2);
             L.act[0] = v[0]; L.act[1] = v[1];
+            auto softplus = [](double z) { return z > 30 ? z : log1p(exp(z)); };
+            L.act[2] = (float) softplus((double) v[0]); L.act[3] = (float) (0.5 + softplus((double) v[1]));      // the two numbers the matmul's epilogue uses
             widen(hy->w_proj, L.ff);
         }
     }

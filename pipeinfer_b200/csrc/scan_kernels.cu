@@ -2,7 +2,6 @@
 //
 //   the pre-norm frame: the residual sum, an RMS norm whose weight is ONE number and the token shift h_t + (h_{t-1} - h_t) * mu in one
 //       pass; embedding rows kept beside the stream for layers that are walked again; the opening [stream ; embedding] of a walk
-//   xIELU: z > 0: a z^2 + z/2;  z <= 0: b (exp(z) - 1 - z) + z/2   (a = softplus(p), b = 1/2 + softplus(q))
 //   the selective state-space scan: per channel c and state n  S <- exp(dt_c A[c][n]) S + dt_c u_c B_n,  y_c = sum_n S C_n + D_c u_c,
 //       dt = softplus(raw + bias), the output gated by silu(z)
 //   the two-branch mixer's per-token work: biases, rotation ("rotate half" pairing) of the first rot_dims coordinates of every query /
@@ -133,28 +132,10 @@ int pib_concat_stream(const float * xin, const float * y, const float * bias, in
     return PIB_OK;
 }
 
-// ---- xIELU, in place on rows [T][F] ----------------------------------------------------------------------------------------------------
-__global__ void xielu_kernel(float * __restrict__ z, int64_t n, float a, float b) {
-    pib_pdl_wait();
-    pib_pdl_trigger();
-    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float v = z[i];
-    z[i] = v > 0.f ? fmaf(a * v, v, 0.5f * v) : fmaf(b, expm1f(v) - v, 0.5f * v);
-}
-int pib_xielu(float * z, int T, int F, float p, float q, cudaStream_t st) {
-    const int64_t n = (int64_t) T * F;
-    if (n <= 0) return PIB_OK;
-    const double sp = p > 20 ? p : log1p(exp((double) p)), sq = q > 20 ? q : log1p(exp((double) q));
-    pib_launch(xielu_kernel, dim3((unsigned) ((n + 255) / 256)), dim3(256), (size_t) 0, st, z, n, (float) sp, (float) (0.5 + sq));
-    CKL();
-    return PIB_OK;
-}
-
 // ---- selective state-space scan --------------------------------------------------------------------------------------------------------
 // grid (segment, tile of SS_THREADS / P channels), SS_THREADS threads: the P lanes of a channel keep states part, part + P, ... in
-// registers (P = 16 for 16 states and more: one state per lane at 16, so that a layer of a few thousand channels fills the machine with
-// warps).  A chunk of SS_TC tokens is staged in shared memory (dt with its bias and softplus applied once per channel and token),
+// registers (P = 16 from 16 states on: one state per lane at 16, so that a layer of a few thousand channels fills the machine with warps;
+// measured at 16 states and 4 096 channels: 4 lanes 0.89 ms, 8 lanes 0.54 ms, 16 lanes 0.46 ms per 2 048 tokens).  A chunk of SS_TC tokens is staged in shared memory (dt with its bias and softplus applied once per channel and token),
 // walked token by token, and its outputs leave in whole rows, gated by silu(z) on the way out.  The states are read from the slot at
 // the segment's start and left there at its end.
 #define SS_THREADS 128
