@@ -57,11 +57,12 @@ def linear_mostly():
 
 
 def walks():
-    """the whole model is one walked run, three walks; then a run of one layer walked twice in front of others"""
-    return model(40, 70, [("mamba1", ssm(48, 4, 3, 2), dense(32)), ("parallel", two(softmax_branch(2, 1, 8, 6, 8), linear_branch(2, 8, 8, [0.7, 0.9])), dense(48))], loop=(0, 2, 3))
+    """the whole model is one walked run, four walks"""
+    return model(40, 70, [("mamba1", ssm(48, 4, 3, 2), dense(32)), ("parallel", two(softmax_branch(2, 1, 8, 6, 8), linear_branch(2, 8, 8, [0.7, 0.9])), dense(48))], loop=(0, 2, 4))
 
 
 def one_layer_walk():
+    """a run of one layer walked twice, between other layers"""
     return model(40, 70, [("parallel", two(softmax_branch(2, 1, 8, 6, 8), linear_branch(2, 8, 8, [0.7, 0.9])), dense(48)),
                           ("mamba1", ssm(48, 4, 3, 2), None), ("mamba1", ssm(24, 5, 2, 4), dense(16))], loop=(1, 2, 2))
 
@@ -86,4 +87,12 @@ def wide_heads():
                            ("parallel", two(softmax_branch(2, 2, 16, 37, 16), linear_branch(2, 16, 24, [0.9, 0.99])), None)], loop=(0, 2, 2))
 
 
-CONFIGS = {f.__name__: f for f in (mixed_small, ssm_only, softmax_mostly, linear_mostly, walks, one_layer_walk, ones, far_keys, wide_heads)}
+def medium():
+    """wider layers in another order: full rotation, more query heads per key head, 16 states, a walked pair in the middle"""
+    return model(128, 500, [("parallel", two(softmax_branch(8, 2, 32, 100, 32, base=1000.0), linear_branch(4, 16, 32, [0.5, 0.9, 0.99, 0.999])), dense(200)),
+                            ("mamba1", ssm(256, 16, 8, 4), dense(160)),
+                            ("parallel", two(softmax_branch(4, 4, 48, 64, 24), linear_branch(2, 32, 16, [0.95, 0.8]), a=0.5, b=1.5), None),
+                            ("mamba1", ssm(192, 8, 6, 3), dense(96))], loop=(1, 3, 2))
+
+
+CONFIGS = {f.__name__: f for f in (medium, mixed_small, ssm_only, softmax_mostly, linear_mostly, walks, one_layer_walk, ones, far_keys, wide_heads)}

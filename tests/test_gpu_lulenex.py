@@ -297,6 +297,28 @@ def test_long_portions_take_the_matmul_attention(tmp_path):
     s.close()
 
 
+@pytest.mark.parametrize("float32", [True, False])
+def test_medium_model_long_prompt_cuts_and_batches(tmp_path, float32):
+    """a wider model with its layers in another order: a prompt over several chunks whole, cut (long portions, short ones, decoded tokens),
+    and two requests sharing batches -- both compute types"""
+    cfg = CONFIGS["medium"]()
+    W = O.random_weights(cfg, 33)
+    toks, other = tokens(cfg, 330, 12), tokens(cfg, 140, 13)
+    ref, ref_o = oracle_logits(cfg, W, toks), oracle_logits(cfg, W, other)
+    tol = TOL32 if float32 else TOL16
+    s = Served(tmp_path, cfg, W, float32=float32, n_ctx=1400)
+    assert row_err(s.feed(0, toks, []), ref).max() < tol
+    assert row_err(s.feed(1, toks, [150, 151, 153, 290] + list(range(300, 330))), ref).max() < tol
+    s.end(0)
+    s.end(1)
+    a = s.step([(2, toks[:129]), (3, other[:7])])
+    b = s.step([(3, other[7:139]), (2, toks[129:131])])
+    c = s.step([(2, toks[131:]), (3, other[139:])])
+    assert row_err(np.concatenate([a[2], b[2], c[2]]), ref).max() < tol
+    assert row_err(np.concatenate([a[3], b[3], c[3]]), ref_o).max() < tol
+    s.close()
+
+
 def test_decode_steps_around_growing_prompts(tmp_path):
     """single-token steps are replayed from captured graphs; a later, longer prompt makes the context grow its buffers, and the steps
     after it must not run on the old ones"""
