@@ -465,7 +465,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         const bool upd = keep && (pend_y || pend_b || !have_x);
         RC(HK_PRENORM, 0, (upd ? 16.0 : 12.0) * Td * Wd, pib_prenorm_shift(have_x ? cur : nullptr, pend_y, pend_b, upd ? other : nullptr, g, eps, mu, B, x->state, hy->state_floats,
                                                                          shift_off, W, x->h, st));
-        nk += mu != nullptr;
+        nk += mu != nullptr && T > B.S;
         if (upd) { std::swap(cur, other); have_x = true; pend_y = pend_b = nullptr; }
         return PIB_OK;
     };

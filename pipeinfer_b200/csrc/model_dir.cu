@@ -589,7 +589,9 @@ static pib_model * build_lulenex(const Json & cfg, TensorSource & src, int dtype
         VEC(L.shift, p + "shift", W);
         if (ty->str == "mamba1") {
             L.mixer = PIB_MIXER_SSM;
-            L.inner = (int) jnum(mx, "inner", 0); L.n_state = (int) jnum(mx, "state", 0); L.dt_rank = (int) jnum(mx, "dt_rank", 0); L.taps = (int) jnum(mx, "conv", 1);
+            // sizes the configuration leaves out are read from the tensors' shapes
+            L.inner = (int) jnum(mx, "inner", (double) (src.dim(px + "in", 0, 0) / 2)); L.n_state = (int) jnum(mx, "state", (double) src.dim(px + "A_log", 1, 0));
+            L.dt_rank = (int) jnum(mx, "dt_rank", (double) src.dim(px + "dt", 1, 0)); L.taps = (int) jnum(mx, "conv", (double) src.dim(px + "conv", 1, 1));
             if (L.inner <= 0 || L.n_state <= 0 || L.dt_rank <= 0 || L.taps < 1) { pib_set_error("model: layer %d: inner / state / dt_rank / conv", il); return nullptr; }
             const int64_t I = L.inner, N = L.n_state, R = L.dt_rank;
             MAT(L.ssm_in, px + "in", 2 * I, W);
@@ -609,7 +611,9 @@ static pib_model * build_lulenex(const Json & cfg, TensorSource & src, int dtype
             L.mixer = PIB_MIXER_DUAL;
             const Json * a = mx->get("left"), * b = mx->get("right");
             if (!a || !b) { pib_set_error("model: layer %d: the mixer needs left and right", il); return nullptr; }
-            L.heads = (int) jnum(a, "heads", 0); L.kv_heads = (int) jnum(a, "kv_heads", L.heads); L.dim = (int) jnum(a, "dim", 0); L.vdim = (int) jnum(a, "vdim", L.dim);
+            L.heads = (int) jnum(a, "heads", (double) src.dim(px + "left.sink", 0, 0));
+            L.dim = (int) jnum(a, "dim", L.heads > 0 ? (double) (src.dim(px + "left.q", 0, 0) / L.heads) : 0.0);
+            L.kv_heads = (int) jnum(a, "kv_heads", L.dim > 0 ? (double) src.dim(px + "left.k", 0, (int64_t) L.heads * L.dim) / L.dim : 0.0); L.vdim = (int) jnum(a, "vdim", L.dim);
             if (L.heads <= 0 || L.dim <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) { pib_set_error("model: layer %d: left heads / kv_heads / dim", il); return nullptr; }
             if (L.vdim != L.dim) { pib_set_error("model: layer %d: the values are the keys, so vdim (%d) must equal dim (%d)", il, L.vdim, L.dim); return nullptr; }
             L.scale = (float) jnum(a, "scale", 1.0 / sqrt((double) L.dim));
@@ -618,8 +622,10 @@ static pib_model * build_lulenex(const Json & cfg, TensorSource & src, int dtype
             if (L.window > 0) L.mask = PIB_MASK_CHUNK; else L.window = 1 << 30;             // no mask: every earlier token is seen
             L.rot_base = (float) jnum(rt, "base", 10000.0); L.rot_dims = rt && !rt->is_null() ? (int) jnum(rt, "dims", L.dim) : 0;
             if (L.rot_dims < 0 || L.rot_dims > L.dim || (L.rot_dims & 1)) { pib_set_error("model: layer %d: rot.dims %d of %d", il, L.rot_dims, L.dim); return nullptr; }
-            L.heads2 = (int) jnum(b, "heads", 0); L.dim2 = (int) jnum(b, "dim", 0); L.vdim2 = (int) jnum(b, "vdim", L.dim2);
             const Json * dc = b->get("decay");
+            L.heads2 = (int) jnum(b, "heads", dc && dc->kind == Json::ARR ? (double) dc->arr.size() : 0.0);
+            L.dim2 = (int) jnum(b, "dim", L.heads2 > 0 ? (double) (src.dim(px + "right.q", 0, 0) / L.heads2) : 0.0);
+            L.vdim2 = (int) jnum(b, "vdim", L.heads2 > 0 ? (double) (src.dim(px + "right.v", 0, (int64_t) L.heads2 * L.dim2) / L.heads2) : 0.0);
             if (L.heads2 <= 0 || L.dim2 <= 0 || L.vdim2 <= 0 || !dc || dc->kind != Json::ARR || (int) dc->arr.size() != L.heads2) { pib_set_error("model: layer %d: right heads / dim / vdim / decay", il); return nullptr; }
             L.mix_a = (float) jnum(mx, "left_scale", 1.0); L.mix_b = (float) jnum(mx, "right_scale", 1.0);
             const int64_t H = L.heads, G = L.kv_heads, D = L.dim, H2 = L.heads2, D2 = L.dim2, V2 = L.vdim2;
@@ -656,8 +662,8 @@ static pib_model * build_lulenex(const Json & cfg, TensorSource & src, int dtype
         } else { pib_set_error("model: layer %d: unknown mixer '%s'", il, ty->str.c_str()); return nullptr; }
         if (ml && !ml->is_null()) {
             const Json * kind = ml->get("kind");
-            if (!kind || kind->str != "dense") { pib_set_error("model: layer %d: unknown mlp kind", il); return nullptr; }
-            L.mlp = PIB_MLP_XIELU; L.ff = (int) jnum(ml, "ff", 0);
+            if (kind && kind->str != "dense") { pib_set_error("model: layer %d: unknown mlp kind", il); return nullptr; }
+            L.mlp = PIB_MLP_XIELU; L.ff = (int) jnum(ml, "ff", (double) src.dim(pm + "up", 0, 0));
             if (L.ff <= 0) { pib_set_error("model: layer %d: mlp.ff", il); return nullptr; }
             ONE(L.g2, p + "norm2");
             MAT(L.up, pm + "up", L.ff, W);

@@ -34,8 +34,8 @@ __device__ __forceinline__ float sk_softplus(float z) { return z > 20.f ? z : lo
 // h[t] = n[t] + (n[t - 1] - n[t]) * mu, where n[t - 1] of a segment's first token is the slot's row (zeros at a sequence's start).
 __global__ void __launch_bounds__(256) prenorm_shift_kernel(const float * __restrict__ xin, const float * __restrict__ y, const float * __restrict__ bias, float * __restrict__ xout,
                                                             float g, float eps, const float * __restrict__ mu, const int32_t * __restrict__ seg,
-                                                            const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot, const float * __restrict__ state,
-                                                            size_t state_stride, size_t shift_off, int W, float * __restrict__ h) {
+                                                            const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot,
+                                                            float * __restrict__ state, size_t state_stride, size_t shift_off, int W, float * __restrict__ h) {
     pib_pdl_wait();
     pib_pdl_trigger();
     extern __shared__ float srow[];               // [2][W]: this token's row, the previous token's
@@ -54,15 +54,18 @@ __global__ void __launch_bounds__(256) prenorm_shift_kernel(const float * __rest
     const float inv0 = g / sqrtf(sk_block_sum(s0, red) / W + eps);
     float inv1 = 0.f;
     if (inside) inv1 = g / sqrtf(sk_block_sum(s1, red) / W + eps);
-    const float * prev = mu ? state + (size_t) seg_slot[seg[t]] * state_stride + shift_off : nullptr;
+    float * prev = mu ? state + (size_t) seg_slot[seg[t]] * state_stride + shift_off : nullptr;
+    const bool single = mu && seg_len[seg[t]] == 1;          // a decoded token: this block is the only reader of the slot's row and leaves its own there
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         const float n = srow[i] * inv0;
         float o = n;
         if (mu) { const float pn = inside ? srow[W + i] * inv1 : prev[i]; o = fmaf(pn - n, mu[i], n); }
         h[(size_t) t * W + i] = o;
+        if (single) prev[i] = n;
     }
 }
-// after prenorm_shift_kernel: the normed (unshifted) row of every segment's last token becomes its slot's previous row
+// after prenorm_shift_kernel, when some segment has more than one token (its first token's block reads the slot's row, so its last token's
+// block cannot replace it in the same launch): the normed (unshifted) row of every segment's last token becomes its slot's previous row
 __global__ void __launch_bounds__(256) prenorm_tail_kernel(const float * __restrict__ xin, const float * __restrict__ y, const float * __restrict__ bias, float g, float eps,
                                                            const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot,
                                                            float * __restrict__ state, size_t state_stride, size_t shift_off, int W) {
@@ -86,10 +89,10 @@ __global__ void __launch_bounds__(256) prenorm_tail_kernel(const float * __restr
 int pib_prenorm_shift(const float * xin, const float * y, const float * bias, float * xout, float g, float eps, const float * mu, const pib_hbatch & b, float * state,
                       size_t state_stride, size_t shift_off, int W, float * h, cudaStream_t st) {
     if (xout && xout == xin) { pib_set_error("pre-norm: the updated stream needs a buffer of its own"); return PIB_ERR_ARG; }
-    pib_launch(prenorm_shift_kernel, dim3(b.T), dim3(256), (size_t) 2 * W * 4, st, xin, y, bias, xout, g, eps, mu, b.seg, b.seg_start, b.seg_slot, (const float *) state, state_stride,
+    pib_launch(prenorm_shift_kernel, dim3(b.T), dim3(256), (size_t) 2 * W * 4, st, xin, y, bias, xout, g, eps, mu, b.seg, b.seg_start, b.seg_len, b.seg_slot, state, state_stride,
                shift_off, W, h);
     CKL();
-    if (mu) {
+    if (mu && b.T > b.S) {            // T == S: every segment is one token, the blocks have left their rows themselves
         pib_launch(prenorm_tail_kernel, dim3(b.S), dim3(256), (size_t) W * 4, st, xin, y, bias, g, eps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, shift_off, W);
         CKL();
     }
