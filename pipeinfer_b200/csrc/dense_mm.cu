@@ -141,7 +141,8 @@ __device__ __forceinline__ void mv_rows_body(const mm_dev & a, bool xvec, int z,
 #pragma unroll
     for (int b = 0; b < B; b++) acc[b] = 0.f;
     const int Kv = a.K - a.K % V;
-#pragma unroll 2
+    // few rows: the loop is bound by the weight bytes a warp has in flight, so more trips are opened at once
+#pragma unroll (B <= 2 ? 4 : 2)
     for (int k = lane * V; k < Kv; k += 32 * V) {
         float w[V];
         wvec<WT>::load(W + k, w);

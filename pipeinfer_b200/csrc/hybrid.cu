@@ -39,6 +39,7 @@ struct pib_hybrid_ctx {
     // operands of the matmul form of the attention: keys [NK][row] and transposed latents [R][NKp] (bfloat16), query rows, score rows
     void * am_kb = nullptr, * am_vt = nullptr, * am_p = nullptr; float * am_q = nullptr, * am_s = nullptr;
     size_t am_kb_cap = 0, am_vt_cap = 0, am_q_cap = 0, am_s_cap = 0, am_p_cap = 0;
+    float * split_buf = nullptr; size_t split_cap = 0;     // a long segment of the constant-decay recurrence in parts: the parts' matrices and table
     std::string kv_error;                       // set when a cache op arrived that the states cannot follow
     // per-launch timing (llama_pib_profile_layer(ctx, >= 0) switches it on): CUDA events around every launch of every layer
     struct Rec { int kind; double flops, bytes; cudaEvent_t e0, e1; };
@@ -119,6 +120,8 @@ int pib_hybrid_set_slots(pib_context * c, int n_slots) {
 }
 int pib_hybrid_slots_free(const pib_context * c) { return c->hy ? c->hy->slots.n_free() : 0; }
 
+#define SCAN_SPLIT_MIN 256
+static bool scan_split_enabled() { static const int on = getenv("PIB_SCAN_SPLIT") ? atoi(getenv("PIB_SCAN_SPLIT")) : 1; return on != 0; }
 static bool attn_mm_enabled() { static const int on = getenv("PIB_ATTN_MM") ? atoi(getenv("PIB_ATTN_MM")) : 1; return on != 0; }
 
 // operands of the matmul form of an attention: key rows of `kw` (+ `kx` extra) bfloat16 each, transposed values [kw][2 NKp], query and
@@ -155,7 +158,7 @@ void pib_hybrid_ctx_free(pib_context * c) {
     free_scratch(x);
     if (x->state) cudaFree(x->state);
     if (x->cellmap) cudaFree(x->cellmap);
-    for (void * p : { x->am_kb, x->am_vt, x->am_p, (void *) x->am_q, (void *) x->am_s }) if (p) cudaFree(p);
+    for (void * p : { x->am_kb, x->am_vt, x->am_p, (void *) x->am_q, (void *) x->am_s, (void *) x->split_buf }) if (p) cudaFree(p);
     for (float * p : x->cache) if (p) cudaFree(p);
     for (float2 * p : x->rope) if (p) cudaFree(p);
     for (int i = 0; i < pib_hybrid_ctx::RING; i++) { if (x->meta_host[i]) cudaFreeHost(x->meta_host[i]); if (x->meta_ev[i]) cudaEventDestroy(x->meta_ev[i]); }
@@ -287,11 +290,35 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * L.vdim, x->y, W, PIB_EPI_NONE));
         return PIB_OK;
     };
+    // the attention of cached key / value heads over `q`: per-token kernel, or the matmul form for long portions in served mode
+    auto kv_attend = [&](const pib_hlayer & L, float * cache, int row, float * out) -> int {
+        const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim;
+        const double keys = key_pairs(L.window, L.mask);
+        const bool mm_ok = !exact && D % 8 == 0 && D >= 16 && V >= 16 && attn_mm_enabled();
+        bool any_mm = false, any_simt = false;
+        for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
+        if (any_simt)
+            RC(HK_KVATTN, 2.0 * keys * H * (D + V), 4.0 * keys * G * (D + V) + 4.0 * Td * H * (D + V),
+               pib_kv_attention(x->q, L, B, cache, row, x->cellmap, (int) c->n_ctx, out, any_mm ? B.mmflag : nullptr, st));
+        for (const pib_hseg & g : segs) {
+            if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
+            const int nb = (g.len + MM_ATTN_BLOCK - 1) / MM_ATTN_BLOCK, per = (g.len + nb - 1) / nb;      // blocks of equal size: none is left with a handful of rows
+            for (int o = 0; o < g.len; o += per) {
+                const int nq = std::min(per, g.len - o), p0 = B_pos_host[g.start + o];
+                const int j0 = L.mask == PIB_MASK_CHUNK ? p0 - p0 % L.window : std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
+                if ((rc = grow_attn_mm(c, (size_t) G * std::max(D, V), (size_t) 3 * G * D + V, nq * H, nq * H, NK)) != PIB_OK) return rc;
+                RC(HK_KVATTN_MM, 2.0 * nq * H * (double) NK * (D + 2.0 * V), 2.0 * NK * G * (D + 2.0 * V) + 8.0 * nq * H * (D + V) + 8.0 * nq * H * (double) NK,
+                   pib_kv_attention_mm(x->q, L, B, cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK, x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p,
+                                       out, st));
+                nk += 5;
+            }
+        }
+        return PIB_OK;
+    };
     // windowed attention over cached key / value heads: projections, convolution, norms + value mixing + cache write, attention, output
     auto mixer_swa = [&](const pib_hlayer & L, const float * hin) -> int {
-        const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim, C = (int) L.qkv->N, row = hy->cache_row[L.cache_id];
+        const int H = L.heads, V = L.vdim, C = (int) L.qkv->N, row = hy->cache_row[L.cache_id];
         float * cache = x->cache[L.cache_id];
-        const double keys = key_pairs(L.window);
         RC(HK_QKV, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, C, PIB_EPI_NONE));
         const float * src = x->proj;
         if (L.conv) {
@@ -300,25 +327,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             src = x->cv;
         }
         RC(HK_APREP, 0, 8.0 * Td * C, pib_swa_prep(src, C, L, eps, B, x->q, cache, row, x->vfirst, st));
-        const bool mm_ok = !exact && D % 8 == 0 && D >= 16 && V >= 16 && attn_mm_enabled();
-        bool any_mm = false, any_simt = false;
-        for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
-        if (any_simt)
-            RC(HK_KVATTN, 2.0 * keys * H * (D + V), 4.0 * keys * G * (D + V) + 4.0 * Td * H * (D + V),
-               pib_kv_attention(x->q, L, B, cache, row, x->cellmap, (int) c->n_ctx, x->att, any_mm ? B.mmflag : nullptr, st));
-        for (const pib_hseg & g : segs) {
-            if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
-            const int nb = (g.len + MM_ATTN_BLOCK - 1) / MM_ATTN_BLOCK, per = (g.len + nb - 1) / nb;      // blocks of equal size: none is left with a handful of rows
-            for (int o = 0; o < g.len; o += per) {
-                const int nq = std::min(per, g.len - o), p0 = B_pos_host[g.start + o];
-                const int j0 = std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
-                if ((rc = grow_attn_mm(c, (size_t) G * std::max(D, V), (size_t) 3 * G * D + V, nq * H, nq * H, NK)) != PIB_OK) return rc;
-                RC(HK_KVATTN_MM, 2.0 * nq * H * (double) NK * (D + 2.0 * V), 2.0 * NK * G * (D + 2.0 * V) + 8.0 * nq * H * (D + V) + 8.0 * nq * H * (double) NK,
-                   pib_kv_attention_mm(x->q, L, B, cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK, x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p,
-                                       x->att, st));
-                nk += 5;
-            }
-        }
+        if ((rc = kv_attend(L, cache, row, x->att)) != PIB_OK) return rc;
         RC(HK_AO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
         return PIB_OK;
     };
@@ -353,31 +362,6 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
         return PIB_OK;
     };
-    // the attention of cached key / value heads over `q`: per-token kernel, or the matmul form for long portions in served mode
-    auto kv_attend = [&](const pib_hlayer & L, float * cache, int row, float * out) -> int {
-        const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim;
-        const double keys = key_pairs(L.window, L.mask);
-        const bool mm_ok = !exact && D % 8 == 0 && D >= 16 && V >= 16 && attn_mm_enabled();
-        bool any_mm = false, any_simt = false;
-        for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
-        if (any_simt)
-            RC(HK_KVATTN, 2.0 * keys * H * (D + V), 4.0 * keys * G * (D + V) + 4.0 * Td * H * (D + V),
-               pib_kv_attention(x->q, L, B, cache, row, x->cellmap, (int) c->n_ctx, out, any_mm ? B.mmflag : nullptr, st));
-        for (const pib_hseg & g : segs) {
-            if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
-            const int nb = (g.len + MM_ATTN_BLOCK - 1) / MM_ATTN_BLOCK, per = (g.len + nb - 1) / nb;      // blocks of equal size: none is left with a handful of rows
-            for (int o = 0; o < g.len; o += per) {
-                const int nq = std::min(per, g.len - o), p0 = B_pos_host[g.start + o];
-                const int j0 = L.mask == PIB_MASK_CHUNK ? p0 - p0 % L.window : std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
-                if ((rc = grow_attn_mm(c, (size_t) G * std::max(D, V), (size_t) 3 * G * D + V, nq * H, nq * H, NK)) != PIB_OK) return rc;
-                RC(HK_KVATTN_MM, 2.0 * nq * H * (double) NK * (D + 2.0 * V), 2.0 * NK * G * (D + 2.0 * V) + 8.0 * nq * H * (D + V) + 8.0 * nq * H * (double) NK,
-                   pib_kv_attention_mm(x->q, L, B, cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK, x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p,
-                                       out, st));
-                nk += 5;
-            }
-        }
-        return PIB_OK;
-    };
     // selective state-space scan: u | z in one matmul, convolution + bias + silu on u, [dt | B | C] from u, dt widened to the channels, the scan
     // (softplus, decays, the skip D u and the gate silu(z) inside), output matmul
     auto mixer_ssm = [&](const pib_hlayer & L, const float * hin) -> int {
@@ -401,7 +385,27 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         RC(HK_DUALPROJ, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
         RC(HK_DUALPREP, 0, 8.0 * Td * ldp, pib_dual_prep(x->proj, ldp, L, eps, B, x->rope[L.rope_id], x->q, cache, row, st));
         if ((rc = kv_attend(L, cache, row, x->lat)) != PIB_OK) return rc;
-        RC(HK_DECAYSCAN, 5.0 * Td * H2 * D2 * V2, 4.0 * Td * H2 * (2.0 * D2 + 2.0 * V2), pib_decay_scan(x->proj, ldp, q2, k2, v2, L, B, x->state, hy->state_floats, x->cv, st));
+        // a batch that is one long segment walks the recurrence in several parts at once (a constant decay allows it)
+        int parts = 0, per = 0;
+        if (B.S == 1 && T >= SCAN_SPLIT_MIN && scan_split_enabled()) {
+            static const int max_parts = getenv("PIB_SCAN_PARTS") ? std::max(2, atoi(getenv("PIB_SCAN_PARTS"))) : 8;
+            per = std::max(64, ((T + max_parts - 1) / max_parts + 31) & ~31);
+            parts = (T + per - 1) / per;
+            if (parts < 2) parts = 0;
+        }
+        if (parts) {
+            const size_t need = pib_decay_split_bytes(L, parts);
+            if (need > x->split_cap) {
+                cudaStreamSynchronize(st);
+                if (x->split_buf) cudaFree(x->split_buf);
+                x->split_buf = nullptr; x->split_cap = 0;
+                if (cudaMalloc(&x->split_buf, need + need / 4) != cudaSuccess) { cudaGetLastError(); pib_set_error("decode: out of memory for the recurrence's parts"); return PIB_ERR_NOMEM; }
+                x->split_cap = need + need / 4;
+            }
+        }
+        RC(HK_DECAYSCAN, 5.0 * Td * H2 * D2 * V2, 4.0 * Td * H2 * (2.0 * D2 + 2.0 * V2),
+           pib_decay_scan(x->proj, ldp, q2, k2, v2, L, B, x->state, hy->state_floats, x->cv, st, x->split_buf, parts, per));
+        nk += parts ? 3 : 0;
         RC(HK_DUALGATE, 0, 8.0 * Td * (H * D + 2.0 * H2 * V2), pib_dual_gate(x->lat, x->cv, x->proj, ldp, ga, gb, L, eps, T, x->att, st));
         RC(HK_DUALO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * D + H2 * V2, x->y, W, PIB_EPI_NONE));
         return PIB_OK;

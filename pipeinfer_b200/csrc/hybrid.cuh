@@ -227,6 +227,7 @@ int pib_ssm_scan(const float * u, int ldu, const float * dtr, int lddt, const fl
                  float * state, size_t state_stride, float * out, cudaStream_t st);
 int pib_dual_prep(float * proj, int ldp, const pib_hlayer & L, float eps, const pib_hbatch & b, const float2 * rope, float * q, float * cache, int cache_row, cudaStream_t st);
 int pib_decay_scan(const float * proj, int ldp, int q_off, int k_off, int v_off, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out,
-                   cudaStream_t st);
+                   cudaStream_t st, float * split_buf = nullptr, int parts = 0, int per = 0);
+size_t pib_decay_split_bytes(const pib_hlayer & L, int parts);
 int pib_dual_gate(const float * a, const float * bo, const float * proj, int ldp, int ga_off, int gb_off, const pib_hlayer & L, float eps, int T, float * out, cudaStream_t st);
 int pib_parallel_sum(float * x, const float * mixer, const float * shared, const float * sgl, int ldsg, const float * edn, const int32_t * inv, int top, int T, int W, cudaStream_t st);

@@ -535,14 +535,104 @@ int pib_delta_scan(const float * cv, int ldc, const float * bg, const pib_hlayer
     return lin_scan(1, A, b.S, st);
 }
 
-// linear attention with one constant decay per head: rows proj[t] hold q (H*D) at q_off, k (H*D) at k_off, v (H*V) at v_off, activations applied
+// ---- a long segment of the constant-decay recurrence in parts --------------------------------------------------------------------------
+// With a constant decay the tokens of a segment need not be walked in one chain.  The segment is cut into P parts; part 0 starts from the
+// slot's matrix, every other part from zeros, and all parts are walked at once by lin_scan_kernel (P times the blocks: the recurrence is
+// bound by dependent issue at low occupancy, not by work).  With L_p the matrix part p ends with and n_p its length, the matrix in front of
+// part p is F_(p-1), F_0 = L_0, F_p = c^(n_p) F_(p-1) + L_p, and what token tau of part p >= 1 still lacks is c^(tau+1) F_(p-1)^T q: one small
+// fp32 product per part and head.  The slot's matrix becomes F_(P-1).
+//   buf (floats): L [P][E] | F [P][E], E = H * D * V; then the parts' table (int32): start [P] | length [P] | index [P]
+__global__ void decay_split_prepare_kernel(const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot, const float * __restrict__ state, size_t state_stride,
+                                           size_t state_off, int E, int P, int T, int per, float * __restrict__ Lm, int32_t * __restrict__ table) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < P) { table[i] = seg_start[0] + (int) i * per; table[P + i] = min(per, T - (int) i * per); table[2 * P + i] = (int) i; }
+    if (i >= (int64_t) P * E) return;
+    Lm[i] = i < E ? state[(size_t) seg_slot[0] * state_stride + state_off + i] : 0.f;
+}
+__global__ void decay_split_combine_kernel(const float * __restrict__ Lm, float * __restrict__ F, int E, int DV, int P, const int32_t * __restrict__ table,
+                                           const float * __restrict__ decay, const int32_t * __restrict__ seg_slot, float * __restrict__ state, size_t state_stride, size_t state_off) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= E) return;
+    const float l2 = log2f(decay[e / DV]);
+    float f = Lm[e];
+    F[e] = f;
+    for (int p = 1; p < P; p++) {
+        f = fmaf(exp2f((float) table[P + p] * l2), f, Lm[(size_t) p * E + e]);
+        F[(size_t) p * E + e] = f;
+    }
+    state[(size_t) seg_slot[0] * state_stride + state_off + e] = f;
+}
+// grid (tiles of DF_TT tokens, heads x tiles of DF_VT columns, parts 1 .. P-1): out[t][h][v] += c^(tau+1) sum_d q[t][h][d] F_(p-1)[h][d][v]
+#define DF_TT 32
+#define DF_VT 64
+__global__ void __launch_bounds__(256) decay_split_fixup_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ F, int E, int H, int D, int V,
+                                                                const int32_t * __restrict__ table, int P, const float * __restrict__ decay, float * __restrict__ out) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float fs[];                 // F tile [D][DF_VT], then query rows [DF_TT][D]
+    const int nvt = (V + DF_VT - 1) / DF_VT, p = blockIdx.z + 1, h = blockIdx.y / nvt, v0 = (blockIdx.y % nvt) * DF_VT, t0 = blockIdx.x * DF_TT;
+    const int start = table[p], len = table[P + p];
+    if (t0 >= len) return;
+    float * qs = fs + (size_t) D * DF_VT;
+    const float * Fp = F + (size_t) (p - 1) * E + (size_t) h * D * V;
+    for (int i = threadIdx.x; i < D * DF_VT; i += blockDim.x) { const int d = i / DF_VT, j = i % DF_VT; fs[i] = v0 + j < V ? Fp[(size_t) d * V + v0 + j] : 0.f; }
+    for (int i = threadIdx.x; i < DF_TT * D; i += blockDim.x) { const int t = i / D, d = i % D; qs[i] = t0 + t < len ? q[(size_t) (start + t0 + t) * ldq + (size_t) h * D + d] : 0.f; }
+    __syncthreads();
+    const int vj = threadIdx.x % DF_VT, tg = threadIdx.x / DF_VT;          // 4 groups of 8 tokens
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+    const float * qr = qs + (size_t) tg * 8 * D;
+    for (int d = 0; d < D; d++) {
+        const float f = fs[d * DF_VT + vj];
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] = fmaf(qr[(size_t) i * D + d], f, acc[i]);
+    }
+    if (v0 + vj >= V) return;
+    const float l2 = log2f(decay[h]);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int t = t0 + tg * 8 + i;
+        if (t < len) { float * o = out + (size_t) (start + t) * H * V + (size_t) h * V + v0 + vj; *o = fmaf(exp2f((float) (t + 1) * l2), acc[i], *o); }
+    }
+}
+size_t pib_decay_split_bytes(const pib_hlayer & L, int parts) { return ((size_t) 2 * parts * L.heads2 * L.dim2 * L.vdim2 + 3 * (size_t) parts) * 4 + 64; }
+
+// linear attention with one constant decay per head: rows proj[t] hold q (H*D) at q_off, k (H*D) at k_off, v (H*V) at v_off, activations applied.
+// parts >= 2 (only for a batch that is ONE segment): the segment is walked as `parts` parts of `per` tokens at once; split_buf holds
+// pib_decay_split_bytes(L, parts) bytes
 int pib_decay_scan(const float * proj, int ldp, int q_off, int k_off, int v_off, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out,
-                   cudaStream_t st) {
+                   cudaStream_t st, float * split_buf, int parts, int per) {
     ls_args A;
     A.a = proj + q_off; A.lda = ldp; A.a_hs = L.dim2; A.k = proj + k_off; A.ldk = ldp; A.k_hs = L.dim2; A.w = L.decay; A.ldw = 0; A.v = proj + v_off; A.ldv = ldp; A.u = nullptr;
     A.H = L.heads2; A.G = L.heads2; A.D = L.dim2; A.V = L.vdim2; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
     A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
-    return lin_scan(2, A, b.S, st);
+    if (parts < 2 || !split_buf) return lin_scan(2, A, b.S, st);
+    if (b.S != 1) { pib_set_error("recurrence in parts: the batch must be one segment"); return PIB_ERR_ARG; }
+    const int H = L.heads2, D = L.dim2, V = L.vdim2, E = H * D * V;
+    float * Lm = split_buf, * F = split_buf + (size_t) parts * E;
+    int32_t * table = reinterpret_cast<int32_t *>(split_buf + (size_t) 2 * parts * E);
+    const int64_t n = (int64_t) parts * E;
+    pib_launch(decay_split_prepare_kernel, dim3((unsigned) ((n + 255) / 256)), dim3(256), (size_t) 0, st, b.seg_start, b.seg_slot, (const float *) state, state_stride, L.state_off, E,
+               parts, b.T, per, Lm, table);
+    CKL();
+    A.seg_start = table; A.seg_len = table + parts; A.seg_slot = table + 2 * parts; A.state = Lm; A.state_stride = (size_t) E; A.state_off = 0;
+    int rc = lin_scan(2, A, parts, st);
+    if (rc != PIB_OK) return rc;
+    pib_launch(decay_split_combine_kernel, dim3((unsigned) ((E + 255) / 256)), dim3(256), (size_t) 0, st, (const float *) Lm, F, E, D * V, parts, (const int32_t *) table,
+               (const float *) L.decay, b.seg_slot, state, state_stride, L.state_off);
+    CKL();
+    const size_t smem = ((size_t) D * DF_VT + (size_t) DF_TT * D) * 4;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_split_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    dim3 grid((unsigned) ((per + DF_TT - 1) / DF_TT), (unsigned) (H * ((V + DF_VT - 1) / DF_VT)), (unsigned) (parts - 1));
+    pib_launch(decay_split_fixup_kernel, dim3(grid), dim3(256), (size_t) smem, st, proj + q_off, ldp, (const float *) F, E, H, D, V, (const int32_t *) table, parts,
+               (const float *) L.decay, out);
+    CKL();
+    return PIB_OK;
 }
 
 // one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w[(h * w_hs) + i] * silu(gate[t * ldg + h * V + i])

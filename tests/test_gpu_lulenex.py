@@ -319,6 +319,23 @@ def test_medium_model_long_prompt_cuts_and_batches(tmp_path, float32):
     s.close()
 
 
+def test_long_segment_walks_the_linear_branch_in_parts(tmp_path):
+    """a batch that is one segment of 256 tokens or more walks the constant-decay recurrence in several parts at once (each part from zeros,
+    then the matrix in front of it is added to its outputs); shorter portions and batches of several requests take the plain walk.  Decays from
+    0.2 to exactly 1; a second long portion starts from the matrix the first one left, and decoding goes on from the combined matrix."""
+    cfg = CONFIGS["linear_mostly"]()
+    W = O.random_weights(cfg, 27)
+    toks = tokens(cfg, 700, 14)
+    ref = oracle_logits(cfg, W, toks)
+    s = Served(tmp_path, cfg, W, n_ctx=2200)
+    whole = s.feed(0, toks, [])                                                    # 8 parts
+    assert row_err(whole, ref).max() < TOL32
+    assert row_err(s.feed(1, toks, [300, 650] + list(range(651, 700))), ref).max() < TOL32      # 5 parts, 6 parts behind them, decoded tokens
+    plain = s.feed(2, toks, range(100, 700, 100))                                  # portions of 100: the plain walk
+    assert row_err(plain, ref).max() < TOL32 and row_err(plain, whole).max() < TOL32
+    s.close()
+
+
 def test_decode_steps_around_growing_prompts(tmp_path):
     """single-token steps are replayed from captured graphs; a later, longer prompt makes the context grow its buffers, and the steps
     after it must not run on the old ones"""
