@@ -69,6 +69,28 @@ def test_whole_prompt_matches_oracle(tmp_path, name, float32):
     assert row_err(got, ref).max() < (TOL32 if float32 else TOL16 * (1.5 if name == "mixed_small" else 1.0))
 
 
+def test_sizes_the_configuration_omits_come_from_tensor_shapes(tmp_path):
+    cfg = CONFIGS["mixed_small"]()
+    W = O.random_weights(cfg, 29)
+    toks = tokens(cfg, 21, 15)
+    ref = oracle_logits(cfg, W, toks)
+    bare = copy.deepcopy(cfg)
+    for l in bare["layers"]:
+        if l["type"] == "mamba1":
+            l["mixer"] = {}
+        else:
+            for k in ("heads", "kv_heads", "dim", "vdim"):
+                l["mixer"]["left"].pop(k)
+            for k in ("heads", "dim", "vdim"):
+                l["mixer"]["right"].pop(k)
+        if l["mlp"]:
+            l["mlp"] = {"kind": "dense"}
+    s = Served(tmp_path, bare, W)
+    got = s.feed(0, toks, [5])
+    s.close()
+    assert row_err(got, ref).max() < TOL32
+
+
 def test_residual_stream_after_every_layer_run(tmp_path, monkeypatch):
     """the library's debugging dump against the oracle's trace: one row block per layer RUN, walks included"""
     cfg = CONFIGS["mixed_small"]()
