@@ -323,7 +323,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         const float * src = x->proj;
         if (L.conv) {
             RC(HK_QKVCONV, 2.0 * Td * C * L.taps, 8.0 * Td * C, pib_chan_conv(x->proj, C, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, C, x->cv, C, 0, 0, st));
-            nk += L.taps > 1;
+            nk += L.taps > 1 && T > B.S;
             src = x->cv;
         }
         RC(HK_APREP, 0, 8.0 * Td * C, pib_swa_prep(src, C, L, eps, B, x->q, cache, row, x->vfirst, st));
@@ -355,7 +355,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim, C = 2 * G * D + H * V, N = (int) L.qkv->N, b_off = C + H * V, a_off = b_off + H;
         RC(HK_QKV, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, N, PIB_EPI_NONE));
         RC(HK_QKVCONV, 2.0 * Td * C * L.taps, 8.0 * Td * C, pib_chan_conv(x->proj, N, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, C, x->cv, C, 0, 1, st));
-        nk += L.taps > 1;
+        nk += L.taps > 1 && T > B.S;
         RC(HK_DPREP, 0, 8.0 * Td * 2 * G * D, pib_delta_prep(x->cv, C, L, x->proj, N, b_off, a_off, x->cq, T, st));
         RC(HK_DSCAN, 8.0 * Td * H * D * V, 4.0 * Td * (C + 2.0 * H + H * V), pib_delta_scan(x->cv, C, x->cq, L, B, x->state, hy->state_floats, x->att, st));
         RC(HK_GHNORM, 0, 12.0 * Td * H * V, pib_gated_head_norm(x->att, T, H, V, L.onorm, 0, x->proj + C, N, eps, st));
@@ -368,7 +368,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         const int I = L.inner, N = L.n_state, R = L.dt_rank, ldx = (R + 2 * N + 3) & ~3;
         RC(HK_SSMIN, mmfl(L.ssm_in), mmby(L.ssm_in), mm(L.ssm_in, hin, W, x->proj, 2 * I, PIB_EPI_NONE));
         RC(HK_SSMCONV, 2.0 * Td * I * L.taps, 8.0 * Td * I, pib_chan_conv(x->proj, 2 * I, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, I, x->cv, I, 0, 1, st, L.conv_b));
-        nk += L.taps > 1;
+        nk += L.taps > 1 && T > B.S;
         RC(HK_SSMX, mmfl(L.ssm_x), mmby(L.ssm_x), mm(L.ssm_x, x->cv, I, x->cq, ldx, PIB_EPI_NONE));
         RC(HK_SSMDT, mmfl(L.ssm_dt), mmby(L.ssm_dt), mm(L.ssm_dt, x->cq, ldx, x->lat, I, PIB_EPI_NONE));
         RC(HK_SSMSCAN, 6.0 * Td * I * N, 4.0 * Td * (4.0 * I + 2.0 * N), pib_ssm_scan(x->cv, I, x->lat, I, x->cq + R, ldx, x->proj + I, 2 * I, L, B, x->state, hy->state_floats, x->att, st));
@@ -505,7 +505,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             } else { pib_set_error("decode: feed-forward %d in a parallel layer", L.mlp); return PIB_ERR_UNSUPP; }
         } else {
             const float * hin = x->x;
-            if (L.canon) { RC(HK_CANON, 2.0 * Td * Wd * hy->taps, 8.0 * Td * Wd, pib_canon_conv(x->x, L.canon, hy->taps, B, x->state, hy->state_floats, L.tail_off, W, x->h, st)); nk += hy->taps > 1; hin = x->h; }
+            if (L.canon) { RC(HK_CANON, 2.0 * Td * Wd * hy->taps, 8.0 * Td * Wd, pib_canon_conv(x->x, L.canon, hy->taps, B, x->state, hy->state_floats, L.tail_off, W, x->h, st)); nk += hy->taps > 1 && T > B.S; hin = x->h; }
             if ((rc = run_mixer(L, hin)) != PIB_OK) return rc;
             RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm1, eps, T, W, x->x, 1, st));
             if (L.mlp == PIB_MLP_POLYNORM) {

@@ -82,15 +82,16 @@ int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, f
 // out[t][c] = (flags & 1 ? u[t][c] : 0) + (bias ? bias[c] : 0) + sum_j w[c][j] * in(t - taps + 1 + j)[c], then silu if flags & 2; in() is this batch's u inside the
 // token's segment, the slot's tail ([taps-1][C]) before it.  u rows have pitch ldu, out rows pitch ldo; C channels.
 #define CANON_MAX_TAPS 16
-enum { CONV_ADD_INPUT = 1, CONV_SILU = 2 };
+enum { CONV_ADD_INPUT = 1, CONV_SILU = 2, CONV_MOVE_TAIL = 4 };
 __global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x, int ldu, const float * __restrict__ w, int taps, const int32_t * __restrict__ seg,
                                                     const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot,
-                                                    const float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h, int ldo, int flags,
+                                                    float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h, int ldo, int flags,
                                                     const float * __restrict__ bias) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int t = blockIdx.x, sg = seg[t], s0 = seg_start[sg];
-    const float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
+    float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
+    const bool single = (flags & CONV_MOVE_TAIL) != 0;    // a batch of decoded tokens only: this block is the tail's only reader and moves it on itself
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float acc = (flags & CONV_ADD_INPUT) ? x[(size_t) t * ldu + c] : 0.f;
         if (bias) acc += bias[c];
@@ -98,13 +99,15 @@ __global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x
             const int tau = t - (taps - 1) + j;
             const float v = tau >= s0 ? x[(size_t) tau * ldu + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
             acc = fmaf(w[(size_t) c * taps + j], v, acc);
+            if (single && j > 0) tail[(size_t) (j - 1) * W + c] = v;      // row j - 1 was read in the trip before: every row moves up one place
         }
         if (flags & CONV_SILU) acc = acc / (1.0f + expf(-acc));
         h[(size_t) t * ldo + c] = acc;
     }
 }
 
-// after canon_kernel: the last taps-1 inputs of every segment become its slot's tail (old tail rows move up when the segment is shorter)
+// after canon_kernel, when some segment has more than one token: the last taps-1 inputs of every segment become its slot's tail (old tail
+// rows move up when the segment is shorter)
 __global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restrict__ x, int ldu, int taps, const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len,
                                                          const int32_t * __restrict__ seg_slot, float * __restrict__ state, size_t state_stride, size_t tail_off, int W) {
     pib_pdl_wait();
@@ -129,10 +132,12 @@ __global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restric
 int pib_chan_conv(const float * u, int ldu, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int C, float * out, int ldo,
                   int add_input, int silu, cudaStream_t st, const float * bias) {
     if (taps > CANON_MAX_TAPS || taps < 1) { pib_set_error("convolution: %d taps (1 to %d)", taps, CANON_MAX_TAPS); return PIB_ERR_UNSUPP; }
-    const int flags = (add_input ? CONV_ADD_INPUT : 0) | (silu ? CONV_SILU : 0);
-    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, u, ldu, w, taps, b.seg, b.seg_start, b.seg_slot, (const float *) state, state_stride, tail_off, C, out, ldo, flags, bias);
+    // T == S: every segment is one token; its block moves the tail on itself and no tail kernel follows.  (In a batch that also holds longer
+    // segments the tail kernel handles every segment, so no block may have moved a tail before it.)
+    const int flags = (add_input ? CONV_ADD_INPUT : 0) | (silu ? CONV_SILU : 0) | (b.T == b.S ? CONV_MOVE_TAIL : 0);
+    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, u, ldu, w, taps, b.seg, b.seg_start, b.seg_slot, state, state_stride, tail_off, C, out, ldo, flags, bias);
     CKL();
-    if (taps > 1) { pib_launch(canon_tail_kernel, dim3(b.S), dim3(256), (size_t) (0), st, u, ldu, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, C); CKL(); }
+    if (taps > 1 && b.T > b.S) { pib_launch(canon_tail_kernel, dim3(b.S), dim3(256), (size_t) (0), st, u, ldu, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, C); CKL(); }
     return PIB_OK;
 }
 // h = x + conv(x) over the model's width, in front of a mixer
