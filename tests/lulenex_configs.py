@@ -95,4 +95,29 @@ def medium():
                             ("mamba1", ssm(192, 8, 6, 3), dense(96))], loop=(1, 3, 2))
 
 
+def drawn(seed):
+    """a configuration drawn from a seed: layer order, every size, the constants and the walked run all vary"""
+    import numpy as np
+    r = np.random.default_rng(seed)
+    pick = lambda xs: xs[int(r.integers(0, len(xs)))]
+    n = int(r.integers(2, 6))
+    layers = []
+    for _ in range(n):
+        if r.random() < 0.45:
+            kind, mx = "mamba1", ssm(pick([16, 40, 56, 96, 160]), pick([1, 3, 8, 16, 24, 40]), int(r.integers(1, 12)), int(r.integers(1, 5)))
+        else:
+            kv, rep, dim = pick([1, 2, 3]), pick([1, 2, 4]), pick([6, 8, 16, 20, 24, 40])
+            left = softmax_branch(kv * rep, kv, dim, pick([1, 3, 16, 50, 129, 1000]), pick([0, 2, dim // 2 // 2 * 2, dim]), base=pick([100.0, 10000.0, 1e6]),
+                                  scale=float(r.uniform(0.5, 2.0)) / math.sqrt(dim))
+            h2 = int(r.integers(1, 4))
+            right = linear_branch(h2, pick([4, 10, 16, 32]), pick([4, 12, 16, 40]), [float(x) for x in r.uniform(0.3, 1.0, h2)])
+            kind, mx = "parallel", two(left, right, a=float(r.uniform(0.3, 1.5)), b=float(r.uniform(0.3, 1.5)))
+        layers.append((kind, mx, dense(pick([16, 50, 128])) if r.random() < 0.7 else None))
+    loop = None
+    if r.random() < 0.7:
+        start = int(r.integers(0, n))
+        loop = (start, int(r.integers(start + 1, n + 1)), int(r.integers(1, 4)))
+    return model(pick([24, 40, 72, 96, 136]), int(r.integers(30, 400)), layers, loop=loop, eps=pick([1e-6, 1e-5]))
+
+
 CONFIGS = {f.__name__: f for f in (medium, mixed_small, ssm_only, softmax_mostly, linear_mostly, walks, one_layer_walk, ones, far_keys, wide_heads)}

@@ -16,7 +16,7 @@ import numpy as np
 import pytest
 
 from tests import lulenex_oracle as O
-from tests.lulenex_configs import CONFIGS
+from tests.lulenex_configs import CONFIGS, drawn
 from tests.test_gpu_rapisun import Served, row_err, spread, TOL32, TOL16
 
 pytestmark = pytest.mark.gpu
@@ -89,6 +89,23 @@ def test_sizes_the_configuration_omits_come_from_tensor_shapes(tmp_path):
     got = s.feed(0, toks, [5])
     s.close()
     assert row_err(got, ref).max() < TOL32
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_drawn_configurations(tmp_path, seed):
+    """configurations drawn from a seed (layer order, sizes that are odd, 1 or large, rotated dimensions from none to all, chunks from 1 to longer
+    than the prompt, walks anywhere): a prompt long enough for the long-segment paths, whole and cut, in float32; whole in bfloat16"""
+    cfg = drawn(100 + seed)
+    W = O.random_weights(cfg, 200 + seed)
+    toks = tokens(cfg, 280, 300 + seed)
+    ref = oracle_logits(cfg, W, toks)
+    s = Served(tmp_path / "a", cfg, W, n_ctx=900)
+    assert row_err(s.feed(0, toks, []), ref).max() < TOL32, json.dumps(cfg)
+    assert row_err(s.feed(1, toks, [2, 131, 132, 260] + list(range(270, 280))), ref).max() < TOL32, json.dumps(cfg)
+    s.close()
+    s = Served(tmp_path / "b", cfg, W, float32=False, n_ctx=300)
+    assert row_err(s.feed(0, toks, []), ref).max() < 2 * TOL16, json.dumps(cfg)
+    s.close()
 
 
 def test_residual_stream_after_every_layer_run(tmp_path, monkeypatch):
