@@ -53,12 +53,14 @@ static const char * const HK_NAMES[] = { "cellmap", "embed_ln", "canon_conv", "m
                                          "embed_scale", "rms_norm_pair", "mm_qkv", "qkv_conv", "attn_prep", "kv_attention", "kv_attention_mm", "token_shift", "mm_rkvg", "mm_decay",
                                          "decay_act", "wkv_scan", "delta_prep", "delta_scan", "gated_head_norm", "glu_clamp", "parallel_sum",
                                          "embed_pair", "prenorm_shift", "loop_concat", "mm_loop_in", "mm_ssm_in", "ssm_conv", "mm_ssm_x", "mm_ssm_dt", "ssm_scan", "mm_ssm_o",
-                                         "mm_dual_proj", "dual_prep", "decay_scan", "dual_gate", "mm_dual_o" };
+                                         "mm_dual_proj", "dual_prep", "decay_scan", "dual_gate", "mm_dual_o",
+                                         "hyper_norm", "mm_mamba2_in", "mamba2_conv", "mamba2_prep", "mamba2_scan", "gated_group_norm", "mm_mamba2_o", "qkv_rope", "diff_combine",
+                                         "mm_gate_up" };
 enum { HK_CELLMAP, HK_EMBED, HK_CANON, HK_DQKV, HK_LPREP, HK_UQ, HK_ABSORB, HK_LATTN, HK_UV, HK_AO, HK_QFV, HK_GATES, HK_SCAN, HK_HO, HK_LNRES, HK_UP, HK_POLY, HK_DOWN,
        HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_LATTN_MM,
        HK_EMBSCALE, HK_NORM2, HK_QKV, HK_QKVCONV, HK_APREP, HK_KVATTN, HK_KVATTN_MM, HK_SHIFT, HK_RKVG, HK_DECAY, HK_DECAYACT, HK_WKVSCAN, HK_DPREP, HK_DSCAN, HK_GHNORM, HK_GLU,
        HK_PSUM, HK_EMBPAIR, HK_PRENORM, HK_CONCAT, HK_LOOPIN, HK_SSMIN, HK_SSMCONV, HK_SSMX, HK_SSMDT, HK_SSMSCAN, HK_SSMO, HK_DUALPROJ, HK_DUALPREP, HK_DECAYSCAN, HK_DUALGATE,
-       HK_DUALO, HK_COUNT };
+       HK_DUALO, HK_HYPER, HK_M2IN, HK_M2CONV, HK_M2PREP, HK_M2SCAN, HK_GGNORM, HK_M2O, HK_QKVROPE, HK_DIFFCOMB, HK_GATEUP, HK_COUNT };
 const char * pib_hybrid_kind_name(int k) { return k >= 0 && k < HK_COUNT ? HK_NAMES[k] : "?"; }
 
 // fetch and clear the records; returns the count (the stream is synchronised)
@@ -96,7 +98,8 @@ int pib_hybrid_ctx_init(pib_context * c, int n_slots) {
     x->rope.assign(hy->ropes.size(), nullptr);
     for (size_t i = 0; i < hy->ropes.size(); i++) {
         std::vector<float2> tab;
-        rope_table_build(tab, (int) c->n_ctx, hy->ropes[i].dims, 4, hy->ropes[i].base, 1.0f);         // mode 4: every angle from its own power, in double
+        if (hy->ropes[i].factor > 0) pib_rope_table(tab, (int) c->n_ctx, hy->ropes[i]);                // scaled frequencies
+        else rope_table_build(tab, (int) c->n_ctx, hy->ropes[i].dims, 4, hy->ropes[i].base, 1.0f);     // mode 4: every angle from its own power, in double
         HCK(cudaMalloc(&x->rope[i], std::max<size_t>(16, tab.size() * sizeof(float2))));
         HCK(cudaMemcpy(x->rope[i], tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice));
     }
@@ -184,11 +187,11 @@ static int grow_scratch(pib_context * c, int T) {
     const size_t n = (size_t) ((T + 63) / 64 * 64), W = (size_t) c->model->n_embd;
     auto fl = [&](float ** p, size_t per) { return per == 0 || cudaMalloc(p, n * per * 4) == cudaSuccess; };
     auto in = [&](int32_t ** p, size_t cnt) { return cnt == 0 || cudaMalloc(p, cnt * 4) == cudaSuccess; };
-    const bool ok = fl(&x->x, W) && fl(&x->h, W) && fl(&x->y, W) && fl(&x->proj, (size_t) hy->w_proj) && fl(&x->cq, (size_t) hy->w_cq) && fl(&x->q, (size_t) hy->w_q) &&
+    const bool ok = fl(&x->x, W * (size_t) hy->streams) && fl(&x->h, W) && fl(&x->y, W) && fl(&x->proj, (size_t) hy->w_proj) && fl(&x->cq, (size_t) hy->w_cq) && fl(&x->q, (size_t) hy->w_q) &&
                     fl(&x->qlat, (size_t) hy->w_lat) && fl(&x->lat, (size_t) hy->w_lat) && fl(&x->att, (size_t) hy->w_att) && fl(&x->rlog, (size_t) hy->w_router) &&
                     fl(&x->wts, (size_t) hy->w_pairs) && fl(&x->eup, (size_t) hy->w_eup) && fl(&x->edn, (size_t) hy->w_pairs * W) && fl(&x->ysh, hy->w_pairs ? W : 0) &&
                     in(&x->ids, n * hy->w_pairs) && in(&x->perm, n * hy->w_pairs) && in(&x->inv, n * hy->w_pairs) && in(&x->counts, (size_t) hy->w_router + 1) &&
-                    in(&x->offs, (size_t) hy->w_router + 2) && fl(&x->h2, hy->form != PIB_FORM_POSTNORM ? W : 0) && fl(&x->cv, (size_t) hy->w_conv) &&
+                    in(&x->offs, (size_t) hy->w_router + 2) && fl(&x->h2, hy->form == PIB_FORM_PARALLEL || hy->form == PIB_FORM_PRENORM ? W : 0) && fl(&x->cv, (size_t) hy->w_conv) &&
                     fl(&x->vfirst, (size_t) hy->w_vfirst) && fl(&x->mixes, (size_t) hy->w_shift) && fl(&x->cat, (size_t) hy->w_cat);
     if (!ok) { cudaGetLastError(); free_scratch(x); pib_set_error("decode: out of memory for the work buffers of %d tokens", T); return PIB_ERR_NOMEM; }
     x->cap = (int) n;
@@ -246,12 +249,15 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         const int H = L.heads, D = L.dim, rd = L.rot_dim, R = L.kv_rank, V = L.vdim, ldp = (int) L.dqkv->N, row = hy->cache_row[L.cache_id];
         float * cache = x->cache[L.cache_id];
         const double keys = key_pairs(L.window);
+        // with a query latent: proj = [W_dq h | W_dkv h], the queries come from the normed latent; without: proj = [W_q h | W_dkv h], the queries stay there
+        const float * qrows = L.q_rank > 0 ? x->q : x->proj;
+        const int     ldq = L.q_rank > 0 ? H * (D + rd) : ldp, kv_off = L.q_rank > 0 ? L.q_rank : H * (D + rd);
         RC(HK_DQKV, mmfl(L.dqkv), mmby(L.dqkv), mm(L.dqkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
-        RC(HK_LPREP, 0, 8.0 * Td * ldp, pib_latent_prep(x->proj, ldp, L, L.dq_norm, L.dkv_norm, eps, B, x->rope[L.rope_id], (int) c->n_ctx, x->cq, L.kv_from < 0 ? cache : nullptr, row, st));
-        RC(HK_UQ, mmfl(L.uq), mmby(L.uq), mm(L.uq, x->cq, L.q_rank, x->q, H * (D + rd), PIB_EPI_NONE));
+        RC(HK_LPREP, 0, 8.0 * Td * ldp, pib_latent_prep(x->proj, ldp, kv_off, L, L.dq_norm, L.dkv_norm, eps, B, x->rope[L.rope_id], (int) c->n_ctx, x->cq, L.kv_from < 0 ? cache : nullptr, row, st));
+        if (L.q_rank > 0) RC(HK_UQ, mmfl(L.uq), mmby(L.uq), mm(L.uq, x->cq, L.q_rank, x->q, H * (D + rd), PIB_EPI_NONE));
         {   // q_lat[t][h] = W_uk,h^T q_unrotated[t][h]: one problem per head
             pib_mm a;
-            a.W = L.ukT->base; a.wtype = L.ukT->type; a.ldw = D; a.wz = (int64_t) R * D; a.X = x->q; a.ldx = (int64_t) H * (D + rd); a.xz = D + rd;
+            a.W = L.ukT->base; a.wtype = L.ukT->type; a.ldw = D; a.wz = (int64_t) R * D; a.X = qrows; a.ldx = ldq; a.xz = D + rd;
             a.Y = x->qlat; a.ldy = (int64_t) H * R; a.yz = R; a.M = T; a.N = R; a.K = D; a.Z = H; a.exact = exact;
             RC(HK_ABSORB, 2.0 * Td * H * R * D, wbytes(L.ukT) + 4.0 * Td * H * (D + R), pib_dense_mm(a, st));
         }
@@ -260,7 +266,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
         if (any_simt)
             RC(HK_LATTN, 4.0 * keys * H * (R + rd), 4.0 * keys * (R + rd) + 8.0 * Td * H * R,
-               pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, any_mm ? B.mmflag : nullptr, st));
+               pib_latent_attention(qrows, ldq, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, any_mm ? B.mmflag : nullptr, st));
         for (const pib_hseg & g : segs) {
             if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
             for (int o = 0; o < g.len; o += MM_ATTN_BLOCK) {
@@ -268,7 +274,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
                 const int j0 = std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
                 if ((rc = grow_attn_mm(c, (size_t) R, (size_t) L.rot_dim, nq * H, nq * H, NK)) != PIB_OK) return rc;
                 RC(HK_LATTN_MM, 2.0 * nq * H * (double) NK * (2.0 * R + rd), 2.0 * NK * (2.0 * R + rd) + 8.0 * nq * H * (2.0 * R + rd) + 8.0 * nq * H * (double) NK,
-                   pib_latent_attention_mm(x->q, x->qlat, L, B, x->rope[L.rope_id], cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK,
+                   pib_latent_attention_mm(qrows, ldq, x->qlat, L, B, x->rope[L.rope_id], cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK,
                                            x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p, x->lat, st));
                 nk += 5;
             }
@@ -292,7 +298,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
     };
     // the attention of cached key / value heads over `q`: per-token kernel, or the matmul form for long portions in served mode
     auto kv_attend = [&](const pib_hlayer & L, float * cache, int row, float * out) -> int {
-        const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim;
+        const int H = L.heads * L.maps, G = L.kv_heads * L.maps, D = L.dim, V = L.vdim;      // query rows and key heads: one per map
         const double keys = key_pairs(L.window, L.mask);
         const bool mm_ok = !exact && D % 8 == 0 && D >= 16 && V >= 16 && attn_mm_enabled();
         bool any_mm = false, any_simt = false;
@@ -410,6 +416,31 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         RC(HK_DUALO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * D + H2 * V2, x->y, W, PIB_EPI_NONE));
         return PIB_OK;
     };
+    // Mamba-2: z | x | B | C | dt in one matmul; convolution + bias + silu over x | B | C; step sizes and decays; the recurrence (with the
+    // skip D x); the gate silu(z) and the RMS norm over equal parts of the channels; output matmul
+    auto mixer_mamba2 = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, I = H * L.vdim, GN = L.kv_heads * L.n_state, C = I + 2 * GN, ldp = ((int) L.ssm_in->N + 3) & ~3;
+        RC(HK_M2IN, mmfl(L.ssm_in), mmby(L.ssm_in), mm(L.ssm_in, hin, W, x->proj, ldp, PIB_EPI_NONE));
+        RC(HK_M2CONV, 2.0 * Td * C * L.taps, 8.0 * Td * C, pib_chan_conv(x->proj + I, ldp, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, C, x->cv, C, 0, 1, st, L.conv_b));
+        nk += L.taps > 1 && T > B.S;
+        RC(HK_M2PREP, 0, 12.0 * Td * H, pib_mamba2_prep(x->proj, ldp, I + C, L, T, x->cq, st));
+        RC(HK_M2SCAN, 5.0 * Td * I * L.n_state, 4.0 * Td * (C + 2.0 * H + I), pib_mamba2_scan(x->cv, C, x->cq, L, B, x->state, hy->state_floats, x->att, st));
+        RC(HK_GGNORM, 0, 12.0 * Td * I, pib_gated_group_norm(x->att, x->proj, ldp, T, I, L.norm_groups, L.onorm, eps, st));
+        RC(HK_M2O, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, I, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
+    // differential attention: q | k | v in one matmul; biases, rotation and the cache write in one kernel; both maps of every head through
+    // the attention of cached key / value heads (a map is a query row of its own over the head's values); a1 - lambda a2 and the unit RMS; output matmul
+    auto mixer_diff = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, V = L.vdim, N = (int) L.qkv->N, ldp = (N + 3) & ~3, row = hy->cache_row[L.cache_id];
+        float * cache = x->cache[L.cache_id];
+        RC(HK_QKV, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+        RC(HK_QKVROPE, 0, 8.0 * Td * N, pib_qkv_rope(x->proj, ldp, L, B, x->rope[L.rope_id], x->q, cache, row, st));
+        if ((rc = kv_attend(L, cache, row, x->lat)) != PIB_OK) return rc;
+        RC(HK_DIFFCOMB, 0, 4.0 * Td * H * V * (L.maps + 1.0), pib_diff_combine(x->lat, L, eps, T, x->att, st));
+        RC(HK_AO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
     auto run_mixer = [&](const pib_hlayer & L, const float * hin) -> int {
         switch (L.mixer) {
             case PIB_MIXER_LATENT: return mixer_latent(L, hin);
@@ -419,6 +450,8 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             case PIB_MIXER_DELTA:  return mixer_delta(L, hin);
             case PIB_MIXER_SSM:    return mixer_ssm(L, hin);
             case PIB_MIXER_DUAL:   return mixer_dual(L, hin);
+            case PIB_MIXER_MAMBA2: return mixer_mamba2(L, hin);
+            case PIB_MIXER_DIFF:   return mixer_diff(L, hin);
         }
         pib_set_error("decode: mixer %d", L.mixer);
         return PIB_ERR_UNSUPP;
@@ -457,7 +490,8 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
     };
 
     RC(HK_CELLMAP, 0, 16.0 * Td, pib_cellmap_set(x->cellmap, (int) c->n_ctx, B, st));
-    if (hy->form == PIB_FORM_PARALLEL)     RC(HK_EMBSCALE, 0, 6.0 * Td * Wd, pib_embed_scale(m->tok_embd, B.tok, hy->embd_scale, T, W, x->x, st));
+    if (hy->form == PIB_FORM_HYPER)        RC(HK_EMBSCALE, 0, (2.0 + 4.0 * hy->streams) * Td * Wd, pib_embed_scale(m->tok_embd, B.tok, hy->embd_scale, T, W, x->x, st, hy->streams));
+    else if (hy->form == PIB_FORM_PARALLEL) RC(HK_EMBSCALE, 0, 6.0 * Td * Wd, pib_embed_scale(m->tok_embd, B.tok, hy->embd_scale, T, W, x->x, st));
     else if (hy->form == PIB_FORM_PRENORM) RC(HK_EMBPAIR, 0, (hy->loops ? 10.0 : 6.0) * Td * Wd, pib_embed_pair(m->tok_embd, B.tok, T, W, x->x, hy->loops ? x->cat : nullptr, st));
     else                                   RC(HK_EMBED, 0, 6.0 * Td * Wd, pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
     // pre-norm form: the stream is (have_x ? cur : 0) + pend_y + pend_b; the sum is formed by the next norm's kernel, which leaves it in the
@@ -476,7 +510,22 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
     for (int il = 0; il < m->n_layer; il++) {
         const pib_hlayer & L = hy->layers[il];
         int lds = 0;
-        if (hy->form == PIB_FORM_PRENORM) {
+        if (hy->form == PIB_FORM_HYPER) {
+            // the write of the sublayer before rides on the kernel that reads and norms the streams for the next one
+            const int Sn = hy->streams;
+            const double hby = (8.0 * Sn + 8.0) * Td * Wd;
+            RC(HK_HYPER, 0, hby, pib_hyper_norm(x->x, Sn, pend_y, pend_b, L.hc1, L.norm1, L.norm1_b, eps, T, W, x->h, st));
+            if ((rc = run_mixer(L, x->h)) != PIB_OK) return rc;
+            pend_y = x->y; pend_b = L.hc1;
+            if (L.mlp == PIB_MLP_GLU) {
+                const int ld = 2 * L.ff;
+                RC(HK_HYPER, 0, hby, pib_hyper_norm(x->x, Sn, pend_y, pend_b, L.hc2, L.norm2, L.norm2_b, eps, T, W, x->h, st));
+                RC(HK_GATEUP, mmfl(L.up), mmby(L.up), mm(L.up, x->h, W, x->proj, ld, PIB_EPI_NONE));
+                RC(HK_GLU, 0, 12.0 * Td * L.ff, pib_glu_clamp(x->proj, ld, L.ff, L.limit_s, nullptr, nullptr, T, st));
+                RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, ld, x->y, W, PIB_EPI_NONE));
+                pend_y = x->y; pend_b = L.hc2;
+            } else if (L.mlp != PIB_MLP_NONE) { pib_set_error("decode: feed-forward %d in a layer with hyper-connections", L.mlp); return PIB_ERR_UNSUPP; }
+        } else if (hy->form == PIB_FORM_PRENORM) {
             if (L.loop_in) {       // a walk opens: x <- W [x ; embedding] + this walk's vector
                 RC(HK_CONCAT, 0, 12.0 * Td * Wd, pib_concat_stream(have_x ? cur : nullptr, pend_y, pend_b, T, W, x->cat, st));
                 RC(HK_LOOPIN, mmfl(L.loop_in), mmby(L.loop_in), mm(L.loop_in, x->cat, 2 * W, x->y, W, PIB_EPI_NONE));
@@ -519,7 +568,16 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
                 RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
             }
         }
-        if (const char * dump = getenv("PIB_HYBRID_DUMP")) {          // debugging: the residual stream after every layer, one file per layer and decode
+        if (getenv("PIB_HYBRID_DUMP") && hy->form == PIB_FORM_HYPER) {   // debugging: the sum of the streams after every layer, one file per layer and decode
+            if (pend_y) { RC(HK_HYPER, 0, 0, pib_hyper_norm(x->x, hy->streams, pend_y, pend_b, nullptr, nullptr, nullptr, eps, T, W, nullptr, st)); pend_y = pend_b = nullptr; }
+            std::vector<float> xb((size_t) T * hy->streams * W), hb((size_t) T * W, 0.f);
+            cudaMemcpyAsync(xb.data(), x->x, xb.size() * 4, cudaMemcpyDeviceToHost, st);
+            cudaStreamSynchronize(st);
+            for (int t = 0; t < T; t++) for (int sn = 0; sn < hy->streams; sn++) for (int i = 0; i < W; i++) hb[(size_t) t * W + i] += xb[((size_t) t * hy->streams + sn) * W + i];
+            char path[512];
+            snprintf(path, sizeof(path), "%s/d%llu_l%d.f32", getenv("PIB_HYBRID_DUMP"), (unsigned long long) c->n_decode, il);
+            if (FILE * f = fopen(path, "wb")) { fwrite(hb.data(), 4, hb.size(), f); fclose(f); }
+        } else if (const char * dump = getenv("PIB_HYBRID_DUMP")) {          // debugging: the residual stream after every layer, one file per layer and decode
             std::vector<float> hb((size_t) T * W), yb, bb;
             if (!(hy->form == PIB_FORM_PRENORM && !have_x)) cudaMemcpyAsync(hb.data(), hy->form == PIB_FORM_PRENORM ? cur : x->x, hb.size() * 4, cudaMemcpyDeviceToHost, st);
             if (pend_y) { yb.resize(hb.size()); cudaMemcpyAsync(yb.data(), pend_y, hb.size() * 4, cudaMemcpyDeviceToHost, st); }
@@ -531,7 +589,8 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             if (FILE * f = fopen(path, "wb")) { fwrite(hb.data(), 4, hb.size(), f); fclose(f); }
         }
     }
-    if (hy->form == PIB_FORM_PRENORM)       { if ((rc = prenorm(hy->final_g, nullptr, 0, false)) != PIB_OK) return rc; }
+    if (hy->form == PIB_FORM_HYPER)         RC(HK_FINAL, 0, (4.0 * hy->streams + 8.0) * Td * Wd, pib_hyper_norm(x->x, hy->streams, pend_y, pend_b, nullptr, m->output_norm, hy->final_b, eps, T, W, x->h, st));
+    else if (hy->form == PIB_FORM_PRENORM)  { if ((rc = prenorm(hy->final_g, nullptr, 0, false)) != PIB_OK) return rc; }
     else if (hy->form == PIB_FORM_PARALLEL) RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_rms_norm2(x->x, m->output_norm, nullptr, eps, hy->logit_scale, T, W, x->h, nullptr, st));
     else                                    RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
     RC(HK_HEAD, mmfl(m->output), mmby(m->output), mm(m->output, x->h, W, run.logits, m->n_vocab, PIB_EPI_NONE));

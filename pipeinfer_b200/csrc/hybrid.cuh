@@ -9,9 +9,16 @@
 //                  weights renormalised or not, on the experts' outputs or inputs, relu^2 or clamped gated experts)
 //   layer forms:   sequential with LayerNorm on the sublayers' outputs; parallel with two RMS norms of the same input; sequential
 //                  pre-norm (RMS norm with ONE number as its weight) with a token shift in front of every mixer
+//                  hyper-connections: several residual streams; a sublayer reads a weighted sum of them through a LayerNorm with weight
+//                  and bias, and every stream becomes a mix of the old streams plus its own multiple of the sublayer's output
 //   layer runs:    a run of layers may be walked several times with the same weights, each walk with a cache and state of its own and
-//                  opened by a projection of [stream ; embedding] plus a learned vector per walk
-// Designs built from these parts: "Rapisun", "Fabivik", "Lulenex".  The parts take their sizes and constants as parameters so that another
+//                  (optionally) opened by a projection of [stream ; embedding] plus a learned vector per walk
+//   more mixers:   Mamba-2 (state-space duality: one decay per head and token, keys / queries shared by groups of heads, gate before a
+//                  grouped RMS norm); differential attention (two softmax maps per head over the same values, subtracted, per-head unit
+//                  RMS; biases, partial rotation with YaRN-scaled frequencies); latent attention without a query latent or sink, rotated
+//                  in adjacent pairs
+//   more feed-forwards: dense clamped gated (the experts' activation of the mixtures above as one dense block)
+// Designs built from these parts: "Rapisun", "Fabivik", "Lulenex", "Putazen".  The parts take their sizes and constants as parameters so that another
 // layer-list design can name them too.
 //
 // What such a model adds to the runtime, beside what llama / falcon graphs use:
@@ -25,15 +32,20 @@
 
 #include "engine.cuh"
 
-enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2, PIB_MIXER_SWA = 3, PIB_MIXER_WKV = 4, PIB_MIXER_DELTA = 5, PIB_MIXER_SSM = 6, PIB_MIXER_DUAL = 7 };
-enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2, PIB_MLP_XIELU = 3 };
+enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2, PIB_MIXER_SWA = 3, PIB_MIXER_WKV = 4, PIB_MIXER_DELTA = 5, PIB_MIXER_SSM = 6, PIB_MIXER_DUAL = 7,
+       PIB_MIXER_MAMBA2 = 8, PIB_MIXER_DIFF = 9 };
+enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2, PIB_MLP_XIELU = 3, PIB_MLP_GLU = 4 };
 // which earlier positions j a token at p may read: the last `window` ones (p - window < j <= p), or those of its own chunk (j / window == p / window)
 enum { PIB_MASK_WINDOW = 0, PIB_MASK_CHUNK = 1 };
 // what a matmul does to an output on its way out: nothing; max(y, 0)^2; xIELU (y > 0: e0 y^2 + y/2, else e1 (exp(y) - 1 - y) + y/2)
 enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1, PIB_EPI_XIELU = 2 };
 // layer forms: x += LN(mixer(conv(x))), x += LN(ff(x))   |   x += mixer(N1(x)) + ff(N2(x)), N = RMS norm with weight (1 + w)
 //              x += mixer(shift(N(x))), x += ff(N(x)), N = RMS norm times one number, shift(h)_t = h_t + (h_{t-1} - h_t) * mu
-enum { PIB_FORM_POSTNORM = 0, PIB_FORM_PARALLEL = 1, PIB_FORM_PRENORM = 2 };
+//              hyper-connections over S streams X_s: u = sum_s in_s X_s, y = sublayer(LN(u)) (LayerNorm with weight and bias),
+//              X_t <- sum_s mix[s][t] X_s + out_t y, for the mixer and then for the feed-forward; the model's output reads sum_s X_s
+enum { PIB_FORM_POSTNORM = 0, PIB_FORM_PARALLEL = 1, PIB_FORM_PRENORM = 2, PIB_FORM_HYPER = 3 };
+// how a rotation pairs coordinates: (i, i + dims / 2) or (2 i, 2 i + 1)
+enum { PIB_PAIR_HALF = 0, PIB_PAIR_ADJACENT = 1 };
 // mixture of experts: how the router's logits become weights, where a weight multiplies, what an expert computes
 enum { PIB_ROUTE_SOFTMAX_RENORM = 0, PIB_ROUTE_SIGMOID = 1 };
 enum { PIB_EXPERT_RELU2 = 0, PIB_EXPERT_GLU_CLAMP = 1 };
@@ -94,6 +106,20 @@ struct pib_hlayer {
     float * decay = nullptr;                          // [heads2]
     float   mix_a = 1.f, mix_b = 1.f;                 // mixer = mix_a * softmax branch + mix_b * linear branch
                                                       // (state_off: the linear branch's matrices [heads2][dim2][vdim2])
+    // ---- hyper-connections (PIB_FORM_HYPER): per sublayer [in (S) | out (S) | mix (S x S, indexed [from][to])]; LayerNorm biases ----
+    float * hc1 = nullptr, * hc2 = nullptr;
+    float * norm1_b = nullptr, * norm2_b = nullptr;
+    // ---- Mamba-2 (PIB_MIXER_MAMBA2): heads x vdim channels, n_state states, kv_heads groups of heads share B and C.  ssm_in rows
+    // [z (I) | x (I) | B (G N) | C (G N) | dt (H)], I = heads * vdim; conv / conv_b over x | B | C (taps); dt_bias, a_log, ssm_d per head;
+    // per head S [n_state][vdim] <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + D x; (y silu(z)) RMS-normed in norm_groups parts, times onorm
+    // (state_off: the matrices [heads][n_state][vdim]; tail_off: the convolution's last taps - 1 inputs) ----
+    int   norm_groups = 1;
+    // ---- differential attention (PIB_MIXER_DIFF): `maps` softmax maps per head over the same values; qkv rows
+    // [q (heads * maps * dim) | k (kv_heads * maps * dim) | v (kv_heads * vdim)], head by head [map 1 | map 2], proj_bias over all rows;
+    // a cell holds [k (kv_heads * maps * dim) | v (kv_heads * vdim)]; o = a1 - diff_lambda a2, o / rms(o) * diff_out ----
+    int   maps = 1;                                   // attention rows per head that share its values (1: ordinary attention)
+    float diff_lambda = 0.f, diff_out = 1.f;
+    int   rot_pairs = PIB_PAIR_HALF;
     // ---- feed-forward ----
     int   ff = 0;
     pib_weight * up = nullptr, * down = nullptr;
@@ -114,6 +140,8 @@ struct pib_hybrid {
     float   eps = 1e-5f;
     float   embd_scale = 1.f, logit_scale = 1.f;      // parallel form: x = embedding * embd_scale, logits = head(norm(x)) * logit_scale
     float * embd_norm = nullptr;
+    int     streams = 1;                              // hyper-connections: residual streams per token
+    float * final_b = nullptr;                        // hyper-connections: the last LayerNorm's bias (its weight is the model's output_norm)
     std::vector<pib_hlayer> layers;
     size_t  state_floats = 0;                         // per state slot
     float   final_g = 1.f;                            // pre-norm form: the last norm's weight
@@ -122,7 +150,10 @@ struct pib_hybrid {
     float * loop_steps = nullptr;                     // [walks][width]
     int     n_cache = 0;
     std::vector<int> cache_row;                       // floats per cell of caching layer i
-    struct Rope { float base; int dims; };
+    // YaRN scaling (factor > 0): with dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0),
+    // hi = min(ceil(dim(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency of pair i is
+    // f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1
+    struct Rope { float base; int dims; double factor = 0, original = 0, fast = 0, slow = 0; };
     std::vector<Rope> ropes;
     // widest per-token scratch rows over all layers
     int     w_proj = 0, w_cq = 0, w_q = 0, w_lat = 0, w_att = 0, w_pairs = 0, w_eup = 0, w_router = 0;
@@ -182,15 +213,18 @@ struct pib_hbatch {                  // device view of one batch's bookkeeping
 };
 int pib_embed_ln(const pib_weight * embd, const int32_t * tok, const float * w, float eps, int T, int W, float * x, cudaStream_t st);
 int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, float * out, int accumulate, cudaStream_t st);
+void pib_rope_table(std::vector<float2> & tab, int n_pos, const pib_hybrid::Rope & r);
 int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int W, float * h,
                    cudaStream_t st);
 int pib_chan_conv(const float * u, int ldu, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int C, float * out, int ldo,
                   int add_input, int silu, cudaStream_t st, const float * bias = nullptr);
-int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
+// kv_off: where W_dkv's rows start in a projection row (the query latent's rank, or the width of the query rows when the layer has no
+// query latent: q_rank 0); ldq: pitch of the query rows [heads][dim + rot_dim]
+int pib_latent_prep(const float * proj, int ldp, int kv_off, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
                     const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st);
-int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
+int pib_latent_attention(const float * q, int ldq, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
                          const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, const int32_t * skip, cudaStream_t st);
-int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
+int pib_latent_attention_mm(const float * q, int ldq, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
                             const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, void * P, float * ctx, cudaStream_t st);
 int pib_window_softmax(float * S, void * P, int NKp, int NK, int j0, int window, const int32_t * pos, int t0, int n_rows, int rows_per_z, int rep, const float * sink,
                        cudaStream_t st, int mask = PIB_MASK_WINDOW);
@@ -204,7 +238,7 @@ int pib_moe_combine(const float * shared, const float * edn, const float * wts, 
 int pib_cellmap_set(int32_t * cellmap, int n_ctx, const pib_hbatch & b, cudaStream_t st);
 
 // mixer_kernels.cu
-int pib_embed_scale(const pib_weight * embd, const int32_t * tok, float scale, int T, int W, float * x, cudaStream_t st);
+int pib_embed_scale(const pib_weight * embd, const int32_t * tok, float scale, int T, int W, float * x, cudaStream_t st, int copies = 1);
 int pib_rms_norm2(const float * x, const float * w1, const float * w2, float eps, float out_scale, int T, int W, float * h1, float * h2, cudaStream_t st);
 int pib_swa_prep(const float * cv, int ldc, const pib_hlayer & L, float eps, const pib_hbatch & b, float * q, float * cache, int cache_row, float * vfirst, cudaStream_t st);
 int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * out,
@@ -230,4 +264,12 @@ int pib_decay_scan(const float * proj, int ldp, int q_off, int k_off, int v_off,
                    cudaStream_t st, float * split_buf = nullptr, int parts = 0, int per = 0);
 size_t pib_decay_split_bytes(const pib_hlayer & L, int parts);
 int pib_dual_gate(const float * a, const float * bo, const float * proj, int ldp, int ga_off, int gb_off, const pib_hlayer & L, float eps, int T, float * out, cudaStream_t st);
+int pib_mamba2_scan(const float * xbc, int ldc, const float * dg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st);
 int pib_parallel_sum(float * x, const float * mixer, const float * shared, const float * sgl, int ldsg, const float * edn, const int32_t * inv, int top, int T, int W, cudaStream_t st);
+// stream_kernels.cu
+int pib_hyper_norm(float * X, int S, const float * y, const float * hc_prev, const float * hc_in, const float * w, const float * bias, float eps, int T, int W, float * h,
+                   cudaStream_t st);
+int pib_mamba2_prep(const float * proj, int ldp, int dt_off, const pib_hlayer & L, int T, float * dg, cudaStream_t st);
+int pib_gated_group_norm(float * y, const float * z, int ldz, int T, int C, int groups, const float * w, float eps, cudaStream_t st);
+int pib_qkv_rope(const float * proj, int ldp, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, float * q, float * cache, int cache_row, cudaStream_t st);
+int pib_diff_combine(const float * a, const pib_hlayer & L, float eps, int T, float * out, cudaStream_t st);

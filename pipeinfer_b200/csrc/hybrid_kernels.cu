@@ -160,10 +160,19 @@ int pib_cellmap_set(int32_t * cellmap, int n_ctx, const pib_hbatch & b, cudaStre
     return PIB_OK;
 }
 
+// coordinate i of a vector whose first rot_dims coordinates turn by the angles cs (pairs (i, i + rot_dims / 2) or (2 i, 2 i + 1))
+__device__ __forceinline__ float rot_coord(const float * __restrict__ v, int i, int rot_dims, int pairs, const float2 * __restrict__ cs) {
+    if (i >= rot_dims) return v[i];
+    if (pairs == PIB_PAIR_ADJACENT) { const float2 c = cs[i >> 1]; return (i & 1) ? v[i] * c.x + v[i - 1] * c.y : v[i] * c.x - v[i + 1] * c.y; }
+    const int half = rot_dims / 2;
+    return i < half ? v[i] * cs[i].x - v[i + half] * cs[i].y : v[i] * cs[i - half].x + v[i - half] * cs[i - half].y;
+}
+
 // ---- latent attention: norms of the two latents, rotation of the shared key part, cache write --------------------------------------
 // proj[t] = [W_dq h (q_rank) | W_dkv h (kv_rank + rot_dim)]; cq[t] = RMSnorm(first part) * dq_norm; with a cache of its own the layer
-// writes cache[cell[t]] = [RMSnorm(next kv_rank) * dkv_norm | rotate(last rot_dim, pos[t])]
-__global__ void __launch_bounds__(128) latent_prep_kernel(const float * __restrict__ proj, int ldp, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+// writes cache[cell[t]] = [RMSnorm(next kv_rank) * dkv_norm | rotate(last rot_dim, pos[t])].  A layer without a query latent (q_rank 0)
+// has its query rows in front instead, kv_off floats wide, and only the cache row is formed.
+__global__ void __launch_bounds__(128) latent_prep_kernel(const float * __restrict__ proj, int ldp, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot_dims, int pairs,
                                                           const float * __restrict__ dq_norm, const float * __restrict__ dkv_norm, float eps,
                                                           const int32_t * __restrict__ pos, const int32_t * __restrict__ cell,
                                                           const float2 * __restrict__ rope, float * __restrict__ cq, float * __restrict__ cache, int cache_row) {
@@ -173,32 +182,27 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const float * __restri
     const int     t = blockIdx.x;
     const float * p = proj + (size_t) t * ldp;
     float s = 0.f;
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) s += p[i] * p[i];
-    const float rq = 1.0f / sqrtf(block_sum(s, red) / q_rank + eps);
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[(size_t) t * q_rank + i] = p[i] * rq * dq_norm[i];
+    if (q_rank > 0) {
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) s += p[i] * p[i];
+        const float rq = 1.0f / sqrtf(block_sum(s, red) / q_rank + eps);
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[(size_t) t * q_rank + i] = p[i] * rq * dq_norm[i];
+    }
     if (!cache) return;
-    const float * d = p + q_rank;
+    const float * d = p + kv_off;
     s = 0.f;
     for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) s += d[i] * d[i];
     const float rc = 1.0f / sqrtf(block_sum(s, red) / kv_rank + eps);
     float * row = cache + (size_t) cell[t] * cache_row;
     for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) row[i] = d[i] * rc * dkv_norm[i];
     const float *  k = d + kv_rank;
-    const int      half = rot_dims / 2;
-    const float2 * cs = rope + (size_t) pos[t] * half;
-    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
-        float v;
-        if (i < half)          v = k[i] * cs[i].x - k[i + half] * cs[i].y;
-        else if (i < rot_dims) v = k[i] * cs[i - half].x + k[i - half] * cs[i - half].y;
-        else                   v = k[i];
-        row[kv_rank + i] = v;
-    }
+    const float2 * cs = rope + (size_t) pos[t] * (rot_dims / 2);
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) row[kv_rank + i] = rot_coord(k, i, rot_dims, pairs, cs);
 }
 
-int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
+int pib_latent_prep(const float * proj, int ldp, int kv_off, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
                     const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st) {
     (void) rope_n_pos;
-    pib_launch(latent_prep_kernel, dim3(b.T), dim3(128), (size_t) (0), st, proj, ldp, L.q_rank, L.kv_rank, L.rot_dim, L.rot_dims, dq_norm, dkv_norm, eps, b.pos, b.cell, rope, cq, cache, cache_row);
+    pib_launch(latent_prep_kernel, dim3(b.T), dim3(128), (size_t) (0), st, proj, ldp, L.q_rank, kv_off, L.kv_rank, L.rot_dim, L.rot_dims, L.rot_pairs, dq_norm, dkv_norm, eps, b.pos, b.cell, rope, cq, cache, cache_row);
     CKL();
     return PIB_OK;
 }
@@ -209,7 +213,7 @@ int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const flo
 // shares of a head are merged in shared memory.  The sink enters as one more logit with no row: the running state starts at
 // (max = sink, denominator = 1, sum = 0).
 template <int RPL>
-__global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int R,
+__global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int pairs, int R,
                                                           float scale, int window, const float * __restrict__ sink, const int32_t * __restrict__ pos,
                                                           const int32_t * __restrict__ slot, const float2 * __restrict__ rope, const float * __restrict__ cache,
                                                           int cache_row, const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ ctx,
@@ -225,15 +229,8 @@ __global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restri
     const bool live = h < H;
     if (live && ks == 0) {
         const float *  qr = q + (size_t) t * ldq + (size_t) h * (D + rot_dim) + D;
-        const int      half = rot_dims / 2;
-        const float2 * cs = rope + (size_t) p * half;
-        for (int i = lane; i < rot_dim; i += 32) {
-            float v;
-            if (i < half)          v = qr[i] * cs[i].x - qr[i + half] * cs[i].y;
-            else if (i < rot_dims) v = qr[i] * cs[i - half].x + qr[i - half] * cs[i - half].y;
-            else                   v = qr[i];
-            qr_s[i] = v;
-        }
+        const float2 * cs = rope + (size_t) p * (rot_dims / 2);
+        for (int i = lane; i < rot_dim; i += 32) qr_s[i] = rot_coord(qr, i, rot_dims, pairs, cs);
     }
     __syncthreads();
     float ql[RPL], acc[RPL];
@@ -242,7 +239,7 @@ __global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restri
         const float * qlp = qlat + ((size_t) t * H + h) * R;
 #pragma unroll
         for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; ql[i] = r < R ? qlp[r] : 0.f; acc[i] = 0.f; }
-        if (ks == 0) { m = sink[h]; l = 1.f; }
+        if (ks == 0 && sink) { m = sink[h]; l = 1.f; }
         const int32_t * map = cellmap + (size_t) slot[t] * n_ctx;
         for (int j = lo + ks; j <= p; j += KS) {
             const float * row = cache + (size_t) map[j] * cache_row;
@@ -286,7 +283,7 @@ __global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restri
     }
 }
 
-int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
+int pib_latent_attention(const float * q, int ldq, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
                          const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, const int32_t * skip, cudaStream_t st) {
     (void) rope_n_pos;
     const int H = L.heads, R = L.kv_rank;
@@ -300,7 +297,7 @@ int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer &
     const int threads = HPB * KS * 32;
 #define LA_GO(RPL) do {                                                                                                            \
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
-        pib_launch(latent_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) (smem), st, q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, L.window, L.sink, b.pos,  \
+        pib_launch(latent_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) (smem), st, q, ldq, qlat, H, L.dim, L.rot_dim, L.rot_dims, L.rot_pairs, R, L.scale, L.window, (const float *) L.sink, b.pos,  \
                                                              b.slot, rope, cache, cache_row, cellmap, n_ctx, HPB, KS, ctx, skip); \
     } while (0)
     if (R <= 128) LA_GO(4); else if (R <= 256) LA_GO(8); else if (R <= 512) LA_GO(16);
@@ -332,7 +329,7 @@ __global__ void __launch_bounds__(128) lat_gather_kernel(const float * __restric
         for (int i = threadIdx.x; i < R; i += blockDim.x) { Vt[(size_t) i * 2 * NKp + j] = __float2bfloat16_rn(0.f); Vt[(size_t) i * 2 * NKp + NKp + j] = __float2bfloat16_rn(0.f); }
     }
 }
-__global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int R,
+__global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int pairs, int R,
                                                        float scale, const int32_t * __restrict__ pos, const float2 * __restrict__ rope, int t0, float * __restrict__ Qc) {
     pib_pdl_wait();
     pib_pdl_trigger();
@@ -341,15 +338,8 @@ __global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict_
     const float * ql = qlat + ((size_t) t * H + h) * R;
     for (int i = threadIdx.x; i < R; i += blockDim.x) out[i] = ql[i] * scale;
     const float *  qr = q + (size_t) t * ldq + (size_t) h * (D + rot_dim) + D;
-    const int      half = rot_dims / 2;
-    const float2 * cs = rope + (size_t) pos[t] * half;
-    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
-        float v;
-        if (i < half)          v = qr[i] * cs[i].x - qr[i + half] * cs[i].y;
-        else if (i < rot_dims) v = qr[i] * cs[i - half].x + qr[i - half] * cs[i - half].y;
-        else                   v = qr[i];
-        out[R + i] = v * scale;
-    }
+    const float2 * cs = rope + (size_t) pos[t] * (rot_dims / 2);
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) out[R + i] = rot_coord(qr, i, rot_dims, pairs, cs) * scale;
 }
 // one score row per (token, head), in place: keys outside [p - window + 1, p] (chunk mask: outside [p - p % window, p]) and the pad get weight 0, the sink (optional) one share of
 // the denominator.  Rows come in groups of rows_per_z (one group per problem of the score matmul), inside a group `rep` heads per token:
@@ -403,12 +393,12 @@ __global__ void lat_widen_kernel(const __nv_bfloat16 * __restrict__ P, int n, fl
 }
 
 // the block of `nq` tokens starting at batch row t0 (positions p0 ..), keys [j0, j0 + NK): ctx rows [(token, head)][R] of those tokens
-int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
+int pib_latent_attention_mm(const float * q, int ldq, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
                             const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, void * P, float * ctx, cudaStream_t st) {
     const int H = L.heads, R = L.kv_rank, RK = R + L.rot_dim, NKp = (NK + 7) & ~7;
     pib_launch(lat_gather_kernel, dim3(NKp), dim3(128), (size_t) (0), st, cache, cache_row, map, j0, NK, NKp, R, RK, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
     CKL();
-    pib_launch(lat_qcat_kernel, dim3(dim3((unsigned) nq, (unsigned) H)), dim3(128), (size_t) (0), st, q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, b.pos, rope, t0, Qc);
+    pib_launch(lat_qcat_kernel, dim3(dim3((unsigned) nq, (unsigned) H)), dim3(128), (size_t) (0), st, q, ldq, qlat, H, L.dim, L.rot_dim, L.rot_dims, L.rot_pairs, R, L.scale, b.pos, rope, t0, Qc);
     CKL();
     pib_mm a;
     a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = NKp; a.M = nq * H; a.N = NK; a.K = RK;

@@ -30,15 +30,19 @@ __device__ __forceinline__ float mk_silu(float z) { return z / (1.0f + expf(-z))
 
 // ---- embedding, norms ------------------------------------------------------------------------------------------------------------
 template <typename WT>
-__global__ void __launch_bounds__(256) embed_scale_kernel(const WT * __restrict__ embd, const int32_t * __restrict__ tok, float scale, int W, float * __restrict__ x) {
+__global__ void __launch_bounds__(256) embed_scale_kernel(const WT * __restrict__ embd, const int32_t * __restrict__ tok, float scale, int W, float * __restrict__ x, int copies) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const WT * r = embd + (size_t) tok[blockIdx.x] * W;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) x[(size_t) blockIdx.x * W + i] = (float) r[i] * scale;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = (float) r[i] * scale;
+        for (int s = 0; s < copies; s++) x[((size_t) blockIdx.x * copies + s) * W + i] = v;
+    }
 }
-int pib_embed_scale(const pib_weight * embd, const int32_t * tok, float scale, int T, int W, float * x, cudaStream_t st) {
-    if (embd->type == PIB_TYPE_BF16) pib_launch(embed_scale_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t) 0, st, (const __nv_bfloat16 *) embd->base, tok, scale, W, x);
-    else                             pib_launch(embed_scale_kernel<float>, dim3(T), dim3(256), (size_t) 0, st, (const float *) embd->base, tok, scale, W, x);
+// copies: every token's row is written that many times, one after the other (the residual streams of hyper-connections start equal)
+int pib_embed_scale(const pib_weight * embd, const int32_t * tok, float scale, int T, int W, float * x, cudaStream_t st, int copies) {
+    if (embd->type == PIB_TYPE_BF16) pib_launch(embed_scale_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t) 0, st, (const __nv_bfloat16 *) embd->base, tok, scale, W, x, copies);
+    else                             pib_launch(embed_scale_kernel<float>, dim3(T), dim3(256), (size_t) 0, st, (const float *) embd->base, tok, scale, W, x, copies);
     CKL();
     return PIB_OK;
 }
@@ -107,7 +111,7 @@ int pib_swa_prep(const float * cv, int ldc, const pib_hlayer & L, float eps, con
 // rows, and the shares of a head are merged in shared memory.  A sink (optional) is one more logit without a row: the running state of
 // share 0 starts at (max = sink, denominator = 1).
 template <int RPL>
-__global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__ q, int H, int G, int D, int V, float scale, int window, int mask, const float * __restrict__ sink,
+__global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__ q, int H, int G, int maps, int D, int V, float scale, int window, int mask, const float * __restrict__ sink,
                                                       const int32_t * __restrict__ pos, const int32_t * __restrict__ slot, const float * __restrict__ cache, int cache_row,
                                                       const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ out,
                                                       const int32_t * __restrict__ skip) {
@@ -122,13 +126,14 @@ __global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__
     float qv[RPL], acc[RPL];
     float m = -INFINITY, l = 0.f;
     if (live) {
-        const int g = h / (H / G);
+        // H counts query rows: `maps` rows per head, next to each other; row h reads map h % maps of its key / value head's keys and that head's values
+        const int g = h / maps / (H / (G * maps)), mp = h % maps;
         const float * qp = q + ((size_t) t * H + h) * D;
 #pragma unroll
         for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; qv[i] = r < D ? qp[r] * scale : 0.f; acc[i] = 0.f; }
         if (ks == 0 && sink) { m = sink[h]; l = 1.f; }
         const int32_t * map = cellmap + (size_t) slot[t] * n_ctx;
-        const size_t ko = (size_t) g * D, vo = (size_t) G * D + (size_t) g * V;
+        const size_t ko = (size_t) (g * maps + mp) * D, vo = (size_t) G * maps * D + (size_t) g * V;
         for (int j = lo + ks; j <= p; j += KS) {
             const float * row = cache + (size_t) map[j] * cache_row;
             float s = 0.f, c[RPL];
@@ -172,7 +177,7 @@ __global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__
 
 int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * out,
                      const int32_t * skip, cudaStream_t st) {
-    const int H = L.heads, V = L.vdim, R = L.dim > L.vdim ? L.dim : L.vdim;
+    const int H = L.heads * L.maps, V = L.vdim, R = L.dim > L.vdim ? L.dim : L.vdim;
     const int HPB = (long long) b.T * H <= 1024 ? 1 : (H < 4 ? H : 4);
     int KS = 16 / HPB;
     if (L.window < 64) KS = 1;
@@ -181,7 +186,7 @@ int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b
     const int threads = HPB * KS * 32;
 #define KA_GO(RPL) do {                                                                                                              \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kv_attn_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);   \
-        pib_launch(kv_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) smem, st, q, H, L.kv_heads, L.dim, V, L.scale, L.window, L.mask, (const float *) L.sink, b.pos, b.slot, cache, \
+        pib_launch(kv_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) smem, st, q, H, L.kv_heads, L.maps, L.dim, V, L.scale, L.window, L.mask, (const float *) L.sink, b.pos, b.slot, cache, \
                    cache_row, cellmap, n_ctx, HPB, KS, out, skip);                                                                  \
     } while (0)
     if (R <= 32) KA_GO(1); else if (R <= 64) KA_GO(2); else if (R <= 128) KA_GO(4); else if (R <= 256) KA_GO(8); else if (R <= 512) KA_GO(16);
@@ -199,63 +204,70 @@ int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b
 // [hi | lo] against the values twice side by side.  These kernels prepare the operands -- keys [G][NKp][3 D], values transposed
 // [G][V][2 NKp], query rows [G][nq * rep][3 D], all bfloat16 -- and put the outputs [G][nq * rep][V] back in token order.
 __device__ __forceinline__ void mk_split(float x, __nv_bfloat16 & hi, __nv_bfloat16 & lo) { hi = __float2bfloat16_rn(x); lo = __float2bfloat16_rn(x - __bfloat162float(hi)); }
-__global__ void __launch_bounds__(128) kv_gather_kernel(const float * __restrict__ cache, int cache_row, const int32_t * __restrict__ map, int j0, int NK, int NKp, int G, int D,
-                                                        int V, __nv_bfloat16 * __restrict__ Kb, __nv_bfloat16 * __restrict__ Vt) {
+__global__ void __launch_bounds__(128) kv_gather_kernel(const float * __restrict__ cache, int cache_row, const int32_t * __restrict__ map, int j0, int NK, int NKp, int G, int maps,
+                                                        int D, int V, __nv_bfloat16 * __restrict__ Kb, __nv_bfloat16 * __restrict__ Vt) {
     pib_pdl_wait();
     pib_pdl_trigger();
-    const int j = blockIdx.x;
+    const int j = blockIdx.x, GK = G * maps;          // one problem per (key / value head, map): its own keys, the head's values
     const float * row = j < NK ? cache + (size_t) map[j0 + j] * cache_row : nullptr;
-    for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    for (int i = threadIdx.x; i < GK * D; i += blockDim.x) {
         __nv_bfloat16 hi, lo;
         mk_split(row ? row[i] : 0.f, hi, lo);
         __nv_bfloat16 * k = Kb + ((size_t) (i / D) * NKp + j) * 3 * D + i % D;
         k[0] = hi; k[D] = hi; k[2 * D] = lo;
     }
-    for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(row ? row[(size_t) G * D + i] : 0.f);
+    for (int i = threadIdx.x; i < GK * V; i += blockDim.x) {
+        const int z = i / V, c = i % V;
+        const __nv_bfloat16 v = __float2bfloat16_rn(row ? row[(size_t) GK * D + (size_t) (z / maps) * V + c] : 0.f);
         Vt[(size_t) i * 2 * NKp + j] = v; Vt[(size_t) i * 2 * NKp + NKp + j] = v;
     }
 }
-// Qc[g][ti * rep + hr] = [hi | lo | hi] of scale * q[t0 + ti][g * rep + hr]
-__global__ void __launch_bounds__(128) kv_query_rows_kernel(const float * __restrict__ q, __nv_bfloat16 * __restrict__ Qc, int H, int rep, int nq, int D, int t0, float scale) {
+// query row h of a token (maps rows per head, next to each other) belongs to problem z = (head / rep) * maps + h % maps, row ti * rep + head % rep
+__device__ __forceinline__ size_t kv_problem_row(int h, int maps, int rep, int nq, int ti) {
+    const int hq = h / maps, z = (hq / rep) * maps + h % maps;
+    return (size_t) z * nq * rep + (size_t) ti * rep + hq % rep;
+}
+// Qc[z][ti * rep + hr] = [hi | lo | hi] of scale * q[t0 + ti][h]
+__global__ void __launch_bounds__(128) kv_query_rows_kernel(const float * __restrict__ q, __nv_bfloat16 * __restrict__ Qc, int H, int maps, int rep, int nq, int D, int t0, float scale) {
     pib_pdl_wait();
     pib_pdl_trigger();
-    const int ti = blockIdx.x, h = blockIdx.y, g = h / rep, hr = h % rep;
+    const int ti = blockIdx.x, h = blockIdx.y;
     const float * src = q + ((size_t) (t0 + ti) * H + h) * D;
-    __nv_bfloat16 * dst = Qc + ((size_t) g * nq * rep + (size_t) ti * rep + hr) * 3 * D;
+    __nv_bfloat16 * dst = Qc + kv_problem_row(h, maps, rep, nq, ti) * 3 * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         __nv_bfloat16 hi, lo;
         mk_split(src[i] * scale, hi, lo);
         dst[i] = hi; dst[D + i] = lo; dst[2 * D + i] = hi;
     }
 }
-// out[t0 + ti][g * rep + hr][V] = O[g][ti * rep + hr][V]
-__global__ void __launch_bounds__(128) kv_token_order_kernel(const float * __restrict__ O, float * __restrict__ out, int H, int rep, int nq, int V, int t0) {
+// out[t0 + ti][h][V] = O[z][ti * rep + hr][V]
+__global__ void __launch_bounds__(128) kv_token_order_kernel(const float * __restrict__ O, float * __restrict__ out, int H, int maps, int rep, int nq, int V, int t0) {
     pib_pdl_wait();
     pib_pdl_trigger();
-    const int ti = blockIdx.x, h = blockIdx.y, g = h / rep, hr = h % rep;
-    const float * src = O + ((size_t) g * nq * rep + (size_t) ti * rep + hr) * V;
+    const int ti = blockIdx.x, h = blockIdx.y;
+    const float * src = O + kv_problem_row(h, maps, rep, nq, ti) * V;
     float * dst = out + ((size_t) (t0 + ti) * H + h) * V;
     for (int i = threadIdx.x; i < V; i += blockDim.x) dst[i] = src[i];
 }
 int pib_kv_attention_mm(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * map, int t0, int nq, int j0, int NK,
                         void * Kb, void * Vt, float * Qc, float * S, void * P, float * out, cudaStream_t st) {
-    const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim, rep = H / G, NKp = (NK + 7) & ~7, M = nq * rep;
-    pib_launch(kv_gather_kernel, dim3(NKp), dim3(128), (size_t) 0, st, cache, cache_row, map, j0, NK, NKp, G, D, V, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
+    const int maps = L.maps, H = L.heads * maps, G = L.kv_heads, GK = G * maps, D = L.dim, V = L.vdim, rep = L.heads / G, NKp = (NK + 7) & ~7, M = nq * rep;
+    if (maps > 1 && L.sink) { pib_set_error("attention: a sink with several maps per head"); return PIB_ERR_UNSUPP; }
+    pib_launch(kv_gather_kernel, dim3(NKp), dim3(128), (size_t) 0, st, cache, cache_row, map, j0, NK, NKp, G, maps, D, V, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
     CKL();
-    pib_launch(kv_query_rows_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, q, (__nv_bfloat16 *) Qc, H, rep, nq, D, t0, L.scale);
+    pib_launch(kv_query_rows_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, q, (__nv_bfloat16 *) Qc, H, maps, rep, nq, D, t0, L.scale);
     CKL();
     pib_mm a;
     a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = 3 * D; a.wz = (int64_t) NKp * 3 * D; a.X = Qc; a.ldx = 3 * D; a.xz = (int64_t) M * 3 * D; a.x_bf16 = 1;
-    a.Y = S; a.ldy = NKp; a.yz = (int64_t) M * NKp; a.M = M; a.N = NK; a.K = 3 * D; a.Z = G;
+    a.Y = S; a.ldy = NKp; a.yz = (int64_t) M * NKp; a.M = M; a.N = NK; a.K = 3 * D; a.Z = GK;
     int rc = pib_dense_mm(a, st);
     if (rc != PIB_OK) return rc;
-    if ((rc = pib_window_softmax(S, P, NKp, NK, j0, L.window, b.pos, t0, G * M, M, rep, L.sink, st, L.mask)) != PIB_OK) return rc;
+    if ((rc = pib_window_softmax(S, P, NKp, NK, j0, L.window, b.pos, t0, GK * M, M, rep, L.sink, st, L.mask)) != PIB_OK) return rc;
     pib_mm v;
     v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.wz = (int64_t) V * 2 * NKp; v.X = (const float *) P; v.ldx = 2 * NKp; v.xz = (int64_t) M * 2 * NKp; v.x_bf16 = 1;
-    v.Y = Qc; v.ldy = V; v.yz = (int64_t) M * V; v.M = M; v.N = V; v.K = 2 * NKp; v.Z = G;               // the query rows are used up: the outputs take their place
+    v.Y = Qc; v.ldy = V; v.yz = (int64_t) M * V; v.M = M; v.N = V; v.K = 2 * NKp; v.Z = GK;              // the query rows are used up: the outputs take their place
     if ((rc = pib_dense_mm(v, st)) != PIB_OK) return rc;
-    pib_launch(kv_token_order_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, (const float *) Qc, out, H, rep, nq, V, t0);
+    pib_launch(kv_token_order_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, (const float *) Qc, out, H, maps, rep, nq, V, t0);
     CKL();
     return PIB_OK;
 }
@@ -350,6 +362,8 @@ int pib_delta_prep(float * cv, int ldc, const pib_hlayer & L, const float * proj
 //   MODE 1 (delta rule):   s_d <- g s_d,  e = beta (v - sum_d s_d k_d),  o = sum_d s_d a_d + e sum_d k_d a_d,  s_d <- s_d + k_d e
 //                                                                                                           row = [a D | k D | v LS_VT | g, beta | dot]
 //   MODE 2 (constant decay): s_d <- c s_d + k_d v,  o = sum_d a_d s_d  (read after the write; c one number per head)   row = [a D | k D | v LS_VT | dot]
+//   MODE 3 (one decay per head and token, Mamba-2): s_d <- c s_d + (dt k_d) v,  o = sum_d a_d s_d + u v  (read after the write; u one number per head)
+//                                                                                                           row = [a D | k D | v LS_VT | c, dt | dot]
 // What does not depend on the matrix or the column -- dot = sum_d a_d u_d k_d (MODE 0), sum_d a_d k_d (MODE 1) -- is formed once per token
 // when its chunk has landed; in MODE 1 the read-out is taken from the sums over the matrix before the write (one round of shuffles for
 // both sums), and the next token's rows are already in registers while the sums of this one cross the lanes.
@@ -358,9 +372,9 @@ int pib_delta_prep(float * cv, int ldc, const pib_hlayer & L, const float * proj
 struct ls_args {
     const float * a; int lda, a_hs;          // query-like rows: a[t * lda + group * a_hs + d]
     const float * k; int ldk, k_hs;
-    const float * w; int ldw;                // MODE 0: decay rows w[t * ldw + h * D + d];   MODE 1: bg rows [beta (H) | g (H)], ldw = 2 H;   MODE 2: decay [H]
+    const float * w; int ldw;                // MODE 0: decay rows w[t * ldw + h * D + d];   MODE 1: bg rows [beta (H) | g (H)], ldw = 2 H;   MODE 2: decay [H];   MODE 3: rows [dt (H) | c (H)]
     const float * v; int ldv;                // v[t * ldv + h * V + j]
-    const float * u;                         // MODE 0: bonus [H][D]
+    const float * u;                         // MODE 0: bonus [H][D];   MODE 3: skip [H]
     int H, G, D, V, chunk;
     const int32_t * seg_start, * seg_len, * seg_slot;
     float * state; size_t state_stride, state_off;
@@ -381,8 +395,8 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
     const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LS_VT, part = threadIdx.x & 15, vl = threadIdx.x >> 4, vd = v0 + vl;
     const int D = FULL ? 16 * RPT : A.D, V = A.V, H = A.H, grp = h / (H / A.G), CH = A.chunk;
     const int s0 = A.seg_start[sg], n = A.seg_len[sg];
-    const int vbase = MODE == 0 ? 3 * D : 2 * D, dot_off = vbase + LS_VT + (MODE == 1 ? 2 : 0), row_f = dot_off + 1;
-    const float cdec = MODE == 2 ? A.w[h] : 0.f;
+    const int vbase = MODE == 0 ? 3 * D : 2 * D, dot_off = vbase + LS_VT + ((MODE == 1 || MODE == 3) ? 2 : 0), row_f = dot_off + 1;
+    const float cdec = MODE == 2 ? A.w[h] : 0.f, skip = MODE == 3 ? A.u[h] : 0.f;
     const bool vok = vd < V;
     float * S = A.state + (size_t) A.seg_slot[sg] * A.state_stride + A.state_off + (size_t) h * D * V;
     float s[RPT], ub[RPT];
@@ -406,7 +420,7 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
             }
             if (threadIdx.x < LS_VT && v0 + (int) threadIdx.x < V)
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (vbase + threadIdx.x)), "l"(A.v + tt * A.ldv + (size_t) h * V + v0 + threadIdx.x) : "memory");
-            if (MODE == 1 && threadIdx.x >= 32 && threadIdx.x < 34) {       // g, then beta
+            if ((MODE == 1 || MODE == 3) && threadIdx.x >= 32 && threadIdx.x < 34) {       // g, then beta (MODE 3: the decay, then dt)
                 const int which = threadIdx.x - 32;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (vbase + LS_VT + which)), "l"(A.w + tt * A.ldw + (which == 0 ? H : 0) + h) : "memory");
             }
@@ -469,6 +483,18 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
                 }
                 acc = ls_sum16(acc);
                 if (part == 0 && vok) *op = fmaf(cdec, acc, v * dot);       // sum_d a_d (c s_d + k_d v)
+            } else if (MODE == 3) {
+                const float dec = sc[LS_VT], kv = sc[LS_VT + 1] * v;
+                float acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; r++) { acc = fmaf(aa[r], s[r], acc); s[r] = fmaf(dec, s[r], kk[r] * kv); }
+#pragma unroll
+                for (int r = 0; r < RPT; r++) {
+                    const bool ok = FULL || part + 16 * r < D;
+                    an[r] = ok ? qn[16 * r] : 0.f; kn[r] = ok ? qn[D + 16 * r] : 0.f; wn[r] = 0.f;
+                }
+                acc = ls_sum16(acc);
+                if (part == 0 && vok) *op = fmaf(dec, acc, fmaf(kv, dot, skip * v));      // sum_d a_d (c s_d + dt k_d v) + u v
             } else {
                 const float g = sc[LS_VT], beta = sc[LS_VT + 1];
                 float sk = 0.f, sa = 0.f;
@@ -499,7 +525,7 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
 static int lin_scan(int mode, ls_args & A, int S, cudaStream_t st) {
     if (A.D > 256) { pib_set_error("recurrence: dim %d not supported (up to 256)", A.D); return PIB_ERR_UNSUPP; }
     dim3 grid((unsigned) S, (unsigned) A.H, (unsigned) ((A.V + LS_VT - 1) / LS_VT));
-    const size_t row_f = (size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + (mode == 1 ? 2 : 0) + 1;
+    const size_t row_f = (size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + ((mode == 1 || mode == 3) ? 2 : 0) + 1;
     // chunks of 32 tokens halve the barriers per token, but their double buffer must not push part of the grid into a second wave
     const size_t smem32 = row_f * 4 * 2 * 32;
     const size_t per_sm = smem32 <= 100 * 1024 ? (size_t) (227 * 1024) / (smem32 + 1024) : 0;
@@ -509,7 +535,7 @@ static int lin_scan(int mode, ls_args & A, int S, cudaStream_t st) {
                                     pib_launch(lin_scan_kernel<RPT, MODE, FULL>, dim3(grid), dim3(16 * LS_VT), (size_t) smem, st, A); } while (0)
 #define LS_PICK(MODE) do { if (A.D == 64) LS_GO(4, MODE, true); else if (A.D == 128) LS_GO(8, MODE, true); else if (A.D <= 32) LS_GO(2, MODE, false); \
                            else if (A.D <= 64) LS_GO(4, MODE, false); else if (A.D <= 128) LS_GO(8, MODE, false); else LS_GO(16, MODE, false); } while (0)
-    if (mode == 0) LS_PICK(0); else if (mode == 1) LS_PICK(1); else LS_PICK(2);
+    if (mode == 0) LS_PICK(0); else if (mode == 1) LS_PICK(1); else if (mode == 2) LS_PICK(2); else LS_PICK(3);
 #undef LS_PICK
 #undef LS_GO
     CKL();
@@ -533,6 +559,16 @@ int pib_delta_scan(const float * cv, int ldc, const float * bg, const pib_hlayer
     A.H = L.heads; A.G = L.kv_heads; A.D = L.dim; A.V = L.vdim; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
     A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
     return lin_scan(1, A, b.S, st);
+}
+
+// Mamba-2: xbc[t] = [x (H*V) | B (G*N) | C (G*N)] after convolution and silu, dg[t] = [dt (H) | decay (H)]; the matrices are [H][N][V]
+int pib_mamba2_scan(const float * xbc, int ldc, const float * dg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st) {
+    const int I = L.heads * L.vdim, GN = L.kv_heads * L.n_state;
+    ls_args A;
+    A.a = xbc + I + GN; A.lda = ldc; A.a_hs = L.n_state; A.k = xbc + I; A.ldk = ldc; A.k_hs = L.n_state; A.w = dg; A.ldw = 2 * L.heads; A.v = xbc; A.ldv = ldc; A.u = L.ssm_d;
+    A.H = L.heads; A.G = L.kv_heads; A.D = L.n_state; A.V = L.vdim; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
+    A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
+    return lin_scan(3, A, b.S, st);
 }
 
 // ---- a long segment of the constant-decay recurrence in parts --------------------------------------------------------------------------

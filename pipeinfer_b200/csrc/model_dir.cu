@@ -713,9 +713,207 @@ static pib_model * build_lulenex(const Json & cfg, TensorSource & src, int dtype
     return mp.release();
 }
 
+// ---- the Putazen builder ----------------------------------------------------------------------------------------------------------
+// Layers with hyper-connections (several residual streams; a sublayer reads a weighted sum of them through a LayerNorm with weight and
+// bias), mixers "mamba2" (state-space duality), "attention" (differential attention: two softmax maps per head, biases, partial rotation in
+// halves with optional YaRN scaling) and "latent_attention" (keys and values from a cached latent, no query latent, rotation in adjacent
+// pairs), dense clamped gated feed-forwards, and an optional "loop": layers start .. stop-1 are walked `times` times with the same
+// tensors, nothing happening between the walks.  The list the runtime walks holds one entry per layer RUN, as for Lulenex.
+// Tensor names: '<layer>.norm1|norm2' (+ '.b'), '<layer>.hc1|hc2.in|out|mix', '<layer>.mix.*', '<layer>.mlp.gate|up|down', 'final.norm' (+ '.b'), 'embed', 'head'.
+static pib_model * build_putazen(const Json & cfg, TensorSource & src, int dtype) {
+    std::unique_ptr<pib_model, void (*)(pib_model *)> mp(new pib_model(), pib_model_free);
+    pib_model * m = mp.get();
+    pib_hybrid * hy = new pib_hybrid();
+    m->hy = hy;
+    m->arch = 2; m->name = "Putazen";
+    bool ok = true;
+    const int W = (int) jnum(&cfg, "width", 0, &ok), V = (int) jnum(&cfg, "vocab", 0, &ok);
+    const Json * layers = cfg.get("layers");
+    if (!ok || W <= 0 || V <= 0 || !layers || layers->kind != Json::ARR || layers->arr.empty()) { pib_set_error("model: config.json needs width, vocab and layers"); return nullptr; }
+    const int n_base = (int) layers->arr.size(), S = (int) jnum(&cfg, "streams", 1);
+    if (S < 1 || S > 16) { pib_set_error("model: streams %d (1 to 16)", S); return nullptr; }
+    hy->dtype = dtype;
+    hy->form = PIB_FORM_HYPER;
+    hy->streams = S;
+    hy->eps = (float) jnum(cfg.get("norm"), "eps", 1e-5);
+    hy->embd_scale = (float) jnum(cfg.get("embedding"), "scale", 1.0);
+    hy->taps = 0;
+    m->n_embd = W; m->n_vocab = V; m->layer_begin = 0;
+    m->wtype = dtype; m->n_ctx_train = 1 << 20; m->n_head = 1; m->n_head_kv = 1; m->tok_bos = -1; m->tok_eos = -1;
+    std::vector<float> v;
+#define GET(name, ...) do { if (!src.get((name), { __VA_ARGS__ }, v)) return nullptr; } while (0)
+#define VEC(dst, name, n) do { GET(name, (int64_t) (n)); if (!((dst) = upload_f32v(v))) return nullptr; } while (0)
+#define MAT(dst, name, N, K) do { GET(name, (int64_t) (N), (int64_t) (K)); if (!((dst) = upload_mat(v, (N), (K), dtype, m))) return nullptr; } while (0)
+#define APPEND(all, name, ...) do { GET(name, __VA_ARGS__); (all).insert((all).end(), v.begin(), v.end()); } while (0)
+    MAT(m->tok_embd, "embed", V, W);
+    VEC(m->output_norm, "final.norm", W);
+    VEC(hy->final_b, "final.norm.b", W);
+    MAT(m->output, "head", V, W);
+    int lp_start = 0, lp_stop = 0, lp_times = 0;
+    const Json * lp = cfg.get("loop");
+    if (lp && !lp->is_null()) {
+        lp_start = (int) jnum(lp, "start", 0); lp_stop = (int) jnum(lp, "stop", 0); lp_times = (int) jnum(lp, "times", 1);
+        if (lp_start < 0 || lp_stop <= lp_start || lp_stop > n_base || lp_times < 1) { pib_set_error("model: loop start %d, stop %d, times %d over %d layers", lp_start, lp_stop, lp_times, n_base); return nullptr; }
+    }
+    auto widen = [](int & a, int64_t b) { if (b > a) a = (int) b; };
+    // [in (S) | out (S) | mix (S x S)] of one sublayer
+    auto hyper = [&](const std::string & pre, float *& dst) -> bool {
+        std::vector<float> all;
+        if (!src.get(pre + "in", { (int64_t) S }, v)) return false;
+        all = v;
+        if (!src.get(pre + "out", { (int64_t) S }, v)) return false;
+        all.insert(all.end(), v.begin(), v.end());
+        if (!src.get(pre + "mix", { (int64_t) S, (int64_t) S }, v)) return false;
+        all.insert(all.end(), v.begin(), v.end());
+        return (dst = upload_f32v(all)) != nullptr;
+    };
+    std::vector<pib_hlayer> base((size_t) n_base);
+    for (int il = 0; il < n_base; il++) {
+        const Json & jl = layers->arr[il];
+        pib_hlayer & L = base[il];
+        const std::string p = "l" + std::to_string(il) + ".", px = p + "mix.", pm = p + "mlp.";
+        const Json * ty = jl.get("type"), * mx = jl.get("mixer"), * ml = jl.get("mlp");
+        if (!ty || ty->kind != Json::STR || !mx) { pib_set_error("model: layer %d needs type and mixer", il); return nullptr; }
+        VEC(L.norm1, p + "norm1", W);
+        VEC(L.norm1_b, p + "norm1.b", W);
+        if (!hyper(p + "hc1.", L.hc1)) return nullptr;
+        L.heads = (int) jnum(mx, "heads", 0); L.vdim = (int) jnum(mx, "vdim", 0);
+        if (L.heads <= 0 || L.vdim <= 0) { pib_set_error("model: layer %d: heads / vdim", il); return nullptr; }
+        const int64_t H = L.heads, Vd = L.vdim;
+        const Json * rt = mx->get("rot");
+        if (ty->str == "mamba2") {
+            L.mixer = PIB_MIXER_MAMBA2;
+            L.n_state = (int) jnum(mx, "state", 0); L.kv_heads = (int) jnum(mx, "groups", 1); L.taps = (int) jnum(mx, "conv", 1); L.norm_groups = (int) jnum(mx, "norm_groups", 1);
+            const int64_t I = H * Vd, GN = (int64_t) L.kv_heads * L.n_state, C = I + 2 * GN;
+            if (L.n_state <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads || L.taps < 1 || L.norm_groups < 1 || I % L.norm_groups) {
+                pib_set_error("model: layer %d: state / groups / conv / norm_groups", il); return nullptr;
+            }
+            MAT(L.ssm_in, px + "in", I + C + H, W);
+            GET(px + "conv", C, (int64_t) L.taps);
+            if (!(L.conv = upload_f32v(v))) return nullptr;
+            VEC(L.conv_b, px + "conv.b", C);
+            VEC(L.dt_bias, px + "dt_bias", H);
+            VEC(L.a_log, px + "A_log", H);
+            VEC(L.ssm_d, px + "D", H);
+            VEC(L.onorm, px + "norm", I);
+            MAT(L.wo, px + "o", W, I);
+            widen(hy->w_proj, (I + C + H + 3) & ~(int64_t) 3); widen(hy->w_conv, C); widen(hy->w_cq, 2 * H); widen(hy->w_att, I);
+        } else if (ty->str == "attention") {
+            L.mixer = PIB_MIXER_DIFF;
+            L.maps = 2;
+            L.dim = (int) jnum(mx, "dim", 0); L.kv_heads = (int) jnum(mx, "kv_heads", L.heads);
+            if (L.dim <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) { pib_set_error("model: layer %d: dim / kv_heads", il); return nullptr; }
+            const int64_t G = L.kv_heads, D = L.dim, NQ = H * 2 * D, NK = G * 2 * D, NV = G * Vd;
+            L.scale = (float) jnum(mx, "scale", 1.0 / sqrt((double) D));
+            L.window = 1 << 30;
+            const double diff = jnum(mx, "diff", 0.0);
+            L.rot_base = (float) jnum(rt, "base", 10000.0); L.rot_dims = rt && !rt->is_null() ? (int) jnum(rt, "dims", (double) D) : 0;
+            L.rot_pairs = PIB_PAIR_HALF;
+            if (L.rot_dims < 0 || L.rot_dims > L.dim || (L.rot_dims & 1)) { pib_set_error("model: layer %d: rot.dims %d of %d", il, L.rot_dims, L.dim); return nullptr; }
+            std::vector<float> all, bias;
+            APPEND(all, px + "q", NQ, W); APPEND(all, px + "k", NK, W); APPEND(all, px + "v", NV, W);
+            if (!(L.qkv = upload_mat(all, NQ + NK + NV, W, dtype, m))) return nullptr;
+            APPEND(bias, px + "q.b", NQ); APPEND(bias, px + "k.b", NK); APPEND(bias, px + "v.b", NV);
+            if (!(L.proj_bias = upload_f32v(bias))) return nullptr;
+            double dots[4];
+            {
+                std::vector<float> a, b;
+                const char * names[4][2] = { { "lq1", "lk1" }, { "lq2", "lk2" } };
+                for (int i = 0; i < 2; i++) {
+                    GET(px + names[i][0], D); a = v;
+                    GET(px + names[i][1], D); b = v;
+                    dots[i] = 0;
+                    for (int64_t d = 0; d < D; d++) dots[i] += (double) a[(size_t) d] * (double) b[(size_t) d];
+                }
+            }
+            L.diff_lambda = (float) (exp(dots[0]) - exp(dots[1]) + diff);       // one number for the layer
+            L.diff_out = (float) (1.0 - diff);
+            MAT(L.wo, px + "o", W, H * Vd);
+            widen(hy->w_proj, (NQ + NK + NV + 3) & ~(int64_t) 3); widen(hy->w_q, NQ); widen(hy->w_lat, H * 2 * Vd); widen(hy->w_att, H * Vd);
+        } else if (ty->str == "latent_attention") {
+            L.mixer = PIB_MIXER_LATENT;
+            L.dim = (int) jnum(mx, "dim", 0); L.rot_dim = (int) jnum(mx, "rot_dim", 0); L.kv_rank = (int) jnum(mx, "kv_rank", 0); L.q_rank = 0;
+            if (L.dim <= 0 || L.rot_dim < 0 || (L.rot_dim & 1) || L.kv_rank <= 0) { pib_set_error("model: layer %d: dim / rot_dim / kv_rank", il); return nullptr; }
+            L.scale = (float) jnum(mx, "scale", 1.0 / sqrt((double) (L.dim + L.rot_dim)));
+            L.window = 1 << 30;
+            L.rot_base = (float) jnum(rt, "base", 10000.0); L.rot_dims = L.rot_dim;              // the rotated vector is the rot_dim part, all of it
+            L.rot_pairs = PIB_PAIR_ADJACENT;
+            const int64_t D = L.dim, rd = L.rot_dim, R = L.kv_rank;
+            std::vector<float> all;
+            APPEND(all, px + "q", H * (D + rd), W); APPEND(all, px + "dkv", R + rd, W);
+            if (!(L.dqkv = upload_mat(all, H * (D + rd) + R + rd, W, dtype, m))) return nullptr;
+            VEC(L.dkv_norm, px + "dkv.norm", R);
+            GET(px + "uk", H * D, R);
+            {   // per head W_uk^T: [kv_rank][dim]
+                std::vector<float> tr((size_t) (H * D * R));
+                for (int64_t h = 0; h < H; h++) for (int64_t d = 0; d < D; d++) for (int64_t r = 0; r < R; r++) tr[(size_t) ((h * R + r) * D + d)] = v[(size_t) ((h * D + d) * R + r)];
+                if (!(L.ukT = upload_mat(tr, H * R, D, dtype, m))) return nullptr;
+            }
+            MAT(L.uv, px + "uv", H * Vd, R);
+            MAT(L.wo, px + "o", W, H * Vd);
+            widen(hy->w_proj, (H * (D + rd) + R + rd + 3) & ~(int64_t) 3); widen(hy->w_lat, H * R); widen(hy->w_att, H * Vd);
+        } else { pib_set_error("model: layer %d: unknown mixer '%s'", il, ty->str.c_str()); return nullptr; }
+        if (ml && !ml->is_null()) {
+            const Json * kind = ml->get("kind");
+            if (kind && kind->str != "dense") { pib_set_error("model: layer %d: unknown mlp kind", il); return nullptr; }
+            L.mlp = PIB_MLP_GLU; L.ff = (int) jnum(ml, "ff", (double) src.dim(pm + "up", 0, 0)); L.limit_s = (float) jnum(ml, "limit", INFINITY);
+            if (L.ff <= 0) { pib_set_error("model: layer %d: mlp.ff", il); return nullptr; }
+            VEC(L.norm2, p + "norm2", W);
+            VEC(L.norm2_b, p + "norm2.b", W);
+            if (!hyper(p + "hc2.", L.hc2)) return nullptr;
+            std::vector<float> all;
+            APPEND(all, pm + "gate", (int64_t) L.ff, W); APPEND(all, pm + "up", (int64_t) L.ff, W);
+            if (!(L.up = upload_mat(all, 2 * (int64_t) L.ff, W, dtype, m))) return nullptr;
+            MAT(L.down, pm + "down", W, L.ff);
+            widen(hy->w_proj, 2 * (int64_t) L.ff);
+        }
+    }
+    // ---- the runs: each with cache rows and state of its own ----
+    std::vector<int> order;
+    for (int il = 0; il < (lp_times ? lp_start : n_base); il++) order.push_back(il);
+    if (lp_times) {
+        for (int r = 0; r < lp_times; r++) for (int il = lp_start; il < lp_stop; il++) order.push_back(il);
+        for (int il = lp_stop; il < n_base; il++) order.push_back(il);
+    }
+    std::vector<int> first((size_t) n_base, -1);
+    size_t state = 0;
+    for (size_t ir = 0; ir < order.size(); ir++) {
+        const int il = order[ir];
+        pib_hlayer L = base[(size_t) il];
+        if (first[(size_t) il] >= 0) L.weights_of = first[(size_t) il]; else first[(size_t) il] = (int) ir;
+        if (L.mixer == PIB_MIXER_MAMBA2) {
+            L.tail_off = state; state += (size_t) (L.taps - 1) * ((size_t) L.heads * L.vdim + 2 * (size_t) L.kv_heads * L.n_state);
+            L.state_off = state; state += (size_t) L.heads * L.n_state * L.vdim;
+        } else {
+            L.cache_id = hy->n_cache++;
+            hy->cache_row.push_back(L.mixer == PIB_MIXER_DIFF ? L.kv_heads * (L.maps * L.dim + L.vdim) : L.kv_rank + L.rot_dim);
+            pib_hybrid::Rope r = { L.rot_base, L.rot_dims };
+            const Json * mx = layers->arr[(size_t) il].get("mixer"), * rt = mx ? mx->get("rot") : nullptr, * sc = rt ? rt->get("scaling") : nullptr;
+            if (L.mixer == PIB_MIXER_DIFF && sc && !sc->is_null()) {
+                r.factor = jnum(sc, "factor", 1.0); r.original = jnum(sc, "original", 1.0); r.fast = jnum(sc, "fast", 32.0); r.slow = jnum(sc, "slow", 1.0);
+                if (!(r.factor > 0) || !(r.original > 0) || !(r.fast > 0) || !(r.slow > 0)) { pib_set_error("model: layer %d: rot.scaling", il); return nullptr; }
+            }
+            L.rope_id = -1;
+            for (size_t i = 0; i < hy->ropes.size(); i++) {
+                const pib_hybrid::Rope & o = hy->ropes[i];
+                if (o.base == r.base && o.dims == r.dims && o.factor == r.factor && o.original == r.original && o.fast == r.fast && o.slow == r.slow) L.rope_id = (int) i;
+            }
+            if (L.rope_id < 0) { L.rope_id = (int) hy->ropes.size(); hy->ropes.push_back(r); }
+        }
+        hy->layers.push_back(L);
+    }
+    m->n_layer = (int) hy->layers.size(); m->layer_end = m->n_layer;
+    hy->state_floats = state ? state : 4;
+#undef GET
+#undef VEC
+#undef MAT
+#undef APPEND
+    return mp.release();
+}
+
 // ---- registry: config.json "architecture" -> builder ---------------------------------------------------------------------------------
 struct DirArch { const char * name; pib_model * (*build)(const Json &, TensorSource &, int); };
-static const DirArch DIR_ARCHS[] = { { "Rapisun", build_rapisun }, { "Fabivik", build_fabivik }, { "Lulenex", build_lulenex } };
+static const DirArch DIR_ARCHS[] = { { "Rapisun", build_rapisun }, { "Fabivik", build_fabivik }, { "Lulenex", build_lulenex }, { "Putazen", build_putazen } };
 
 static pib_model * build_from_config(const Json & cfg, TensorSource & src, int dtype) {
     const Json * a = cfg.get("architecture");
@@ -752,11 +950,12 @@ void pib_hybrid_model_free(pib_model * m) {
     for (pib_hlayer & L : hy->layers) {
         if (L.weights_of >= 0) continue;                  // a later walk of the same layer: the tensors are the first walk's
         for (float * f : { L.norm1, L.norm2, L.canon, L.dq_norm, L.dkv_norm, L.sink, L.f_bias, L.lower, L.onorm, L.conv, L.q_norm, L.k_norm, L.mu, L.w0, L.bonus, L.a_log,
-                           L.dt_bias, L.shift, L.conv_b, L.ssm_a, L.ssm_d, L.proj_bias, L.o_bias, L.decay }) if (f) cudaFree(f);
+                           L.dt_bias, L.shift, L.conv_b, L.ssm_a, L.ssm_d, L.proj_bias, L.o_bias, L.decay, L.hc1, L.hc2, L.norm1_b, L.norm2_b }) if (f) cudaFree(f);
         for (pib_weight * w : { L.dqkv, L.uq, L.ukT, L.uv, L.wo, L.qfv, L.up, L.down, L.e_up, L.e_down, L.router, L.s_up, L.s_down, L.qkv, L.rkvg, L.w1, L.w2, L.ssm_in, L.ssm_x,
                                 L.ssm_dt }) if (w) pib_weight_free(w);
     }
     if (hy->embd_norm) cudaFree(hy->embd_norm);
+    if (hy->final_b) cudaFree(hy->final_b);
     if (hy->loop_in) pib_weight_free(hy->loop_in);
     if (hy->loop_steps) cudaFree(hy->loop_steps);
     delete hy;
