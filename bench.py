@@ -231,9 +231,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-plain", action="store_true", help="skip the non-speculative generation after the timed steps (plain_tok_s, plain_tokens_sha)")
     ap.add_argument("--layer-split", default="", help="comma-separated per-stage weights, as the reference's --mpi-layer-split")
-    ap.add_argument("--design", default="", choices=["", "rapisun", "fabivik", "lulenex"],
+    ap.add_argument("--design", default="", choices=["", "rapisun", "fabivik", "lulenex", "putazen"],
                     help="instead of the default workload: prefill / decode throughput and per-launch rooflines of a layer-list design beside the closest existing model "
-                         "(rapisun: the llama architecture in Q4_K; fabivik: the Rapisun design; lulenex: the Fabivik design)")
+                         "(rapisun: the llama architecture in Q4_K; fabivik: the Rapisun design; lulenex: the Fabivik design; putazen: the Lulenex design)")
     ap.add_argument("--design-size", default="w2048", help="comma-separated sizes of pipeinfer_b200/design_bench.py: w1024, w2048, w4096")
     ap.add_argument("--design-prompt", default="512,2048", help="prompt lengths of the prefill measurement")
     ap.add_argument("--head-share", type=float, default=None, help="share of the target's layers on the head GPU (which also runs the draft)")

@@ -384,15 +384,9 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
     // two branches on the same input: every projection in one matmul; biases, rotation, unit norms, cache write and the linear branch's
     // activations in one kernel; attention over the token's chunk; the constant-decay recurrence; gates, the norm over the linear branch's
     // heads and both scales in one kernel; one output matmul over [softmax branch | linear branch] (its bias joins the residual sum)
-    auto mixer_dual = [&](const pib_hlayer & L, const float * hin) -> int {
-        const int H = L.heads, G = L.kv_heads, D = L.dim, H2 = L.heads2, D2 = L.dim2, V2 = L.vdim2, row = hy->cache_row[L.cache_id];
-        const int ldp = ((int) L.qkv->N + 3) & ~3, ga = (H + G) * D, q2 = ga + H, k2 = q2 + H2 * D2, v2 = k2 + H2 * D2, gb = v2 + H2 * V2;
-        float * cache = x->cache[L.cache_id];
-        RC(HK_DUALPROJ, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
-        RC(HK_DUALPREP, 0, 8.0 * Td * ldp, pib_dual_prep(x->proj, ldp, L, eps, B, x->rope[L.rope_id], x->q, cache, row, st));
-        if ((rc = kv_attend(L, cache, row, x->lat)) != PIB_OK) return rc;
-        // a batch that is one long segment walks the recurrence in several parts at once (a constant decay allows it)
-        int parts = 0, per = 0;
+    // a batch that is one long segment walks a recurrence with scalar decays in several parts at once; this sizes the parts and their buffer
+    auto split_plan = [&](int Hn, int Dn, int Vn, int & parts, int & per) -> int {
+        parts = per = 0;
         if (B.S == 1 && T >= SCAN_SPLIT_MIN && scan_split_enabled()) {
             static const int max_parts = getenv("PIB_SCAN_PARTS") ? std::max(2, atoi(getenv("PIB_SCAN_PARTS"))) : 8;
             per = std::max(64, ((T + max_parts - 1) / max_parts + 31) & ~31);
@@ -400,7 +394,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             if (parts < 2) parts = 0;
         }
         if (parts) {
-            const size_t need = pib_decay_split_bytes(L, parts);
+            const size_t need = pib_scan_split_bytes(Hn, Dn, Vn, parts);
             if (need > x->split_cap) {
                 cudaStreamSynchronize(st);
                 if (x->split_buf) cudaFree(x->split_buf);
@@ -409,6 +403,17 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
                 x->split_cap = need + need / 4;
             }
         }
+        return PIB_OK;
+    };
+    auto mixer_dual = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, G = L.kv_heads, D = L.dim, H2 = L.heads2, D2 = L.dim2, V2 = L.vdim2, row = hy->cache_row[L.cache_id];
+        const int ldp = ((int) L.qkv->N + 3) & ~3, ga = (H + G) * D, q2 = ga + H, k2 = q2 + H2 * D2, v2 = k2 + H2 * D2, gb = v2 + H2 * V2;
+        float * cache = x->cache[L.cache_id];
+        RC(HK_DUALPROJ, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+        RC(HK_DUALPREP, 0, 8.0 * Td * ldp, pib_dual_prep(x->proj, ldp, L, eps, B, x->rope[L.rope_id], x->q, cache, row, st));
+        if ((rc = kv_attend(L, cache, row, x->lat)) != PIB_OK) return rc;
+        int parts = 0, per = 0;
+        if ((rc = split_plan(H2, D2, V2, parts, per)) != PIB_OK) return rc;
         RC(HK_DECAYSCAN, 5.0 * Td * H2 * D2 * V2, 4.0 * Td * H2 * (2.0 * D2 + 2.0 * V2),
            pib_decay_scan(x->proj, ldp, q2, k2, v2, L, B, x->state, hy->state_floats, x->cv, st, x->split_buf, parts, per));
         nk += parts ? 3 : 0;
@@ -424,7 +429,10 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         RC(HK_M2CONV, 2.0 * Td * C * L.taps, 8.0 * Td * C, pib_chan_conv(x->proj + I, ldp, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, C, x->cv, C, 0, 1, st, L.conv_b));
         nk += L.taps > 1 && T > B.S;
         RC(HK_M2PREP, 0, 12.0 * Td * H, pib_mamba2_prep(x->proj, ldp, I + C, L, T, x->cq, st));
-        RC(HK_M2SCAN, 5.0 * Td * I * L.n_state, 4.0 * Td * (C + 2.0 * H + I), pib_mamba2_scan(x->cv, C, x->cq, L, B, x->state, hy->state_floats, x->att, st));
+        int parts = 0, per = 0;
+        if ((rc = split_plan(H, L.n_state, L.vdim, parts, per)) != PIB_OK) return rc;
+        RC(HK_M2SCAN, 5.0 * Td * I * L.n_state, 4.0 * Td * (C + 2.0 * H + I), pib_mamba2_scan(x->cv, C, x->cq, L, B, x->state, hy->state_floats, x->att, st, x->split_buf, parts, per));
+        nk += parts ? 4 : 0;
         RC(HK_GGNORM, 0, 12.0 * Td * I, pib_gated_group_norm(x->att, x->proj, ldp, T, I, L.norm_groups, L.onorm, eps, st));
         RC(HK_M2O, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, I, x->y, W, PIB_EPI_NONE));
         return PIB_OK;

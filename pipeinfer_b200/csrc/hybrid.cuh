@@ -264,7 +264,9 @@ int pib_decay_scan(const float * proj, int ldp, int q_off, int k_off, int v_off,
                    cudaStream_t st, float * split_buf = nullptr, int parts = 0, int per = 0);
 size_t pib_decay_split_bytes(const pib_hlayer & L, int parts);
 int pib_dual_gate(const float * a, const float * bo, const float * proj, int ldp, int ga_off, int gb_off, const pib_hlayer & L, float eps, int T, float * out, cudaStream_t st);
-int pib_mamba2_scan(const float * xbc, int ldc, const float * dg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st);
+int pib_mamba2_scan(const float * xbc, int ldc, float * dg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st,
+                    float * split_buf = nullptr, int parts = 0, int per = 0);
+size_t pib_scan_split_bytes(int H, int D, int V, int parts);
 int pib_parallel_sum(float * x, const float * mixer, const float * shared, const float * sgl, int ldsg, const float * edn, const int32_t * inv, int top, int T, int W, cudaStream_t st);
 // stream_kernels.cu
 int pib_hyper_norm(float * X, int S, const float * y, const float * hc_prev, const float * hc_in, const float * w, const float * bias, float eps, int T, int W, float * h,

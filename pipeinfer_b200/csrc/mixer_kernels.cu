@@ -561,16 +561,6 @@ int pib_delta_scan(const float * cv, int ldc, const float * bg, const pib_hlayer
     return lin_scan(1, A, b.S, st);
 }
 
-// Mamba-2: xbc[t] = [x (H*V) | B (G*N) | C (G*N)] after convolution and silu, dg[t] = [dt (H) | decay (H)]; the matrices are [H][N][V]
-int pib_mamba2_scan(const float * xbc, int ldc, const float * dg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st) {
-    const int I = L.heads * L.vdim, GN = L.kv_heads * L.n_state;
-    ls_args A;
-    A.a = xbc + I + GN; A.lda = ldc; A.a_hs = L.n_state; A.k = xbc + I; A.ldk = ldc; A.k_hs = L.n_state; A.w = dg; A.ldw = 2 * L.heads; A.v = xbc; A.ldv = ldc; A.u = L.ssm_d;
-    A.H = L.heads; A.G = L.kv_heads; A.D = L.n_state; A.V = L.vdim; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
-    A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
-    return lin_scan(3, A, b.S, st);
-}
-
 // ---- a long segment of the constant-decay recurrence in parts --------------------------------------------------------------------------
 // With a constant decay the tokens of a segment need not be walked in one chain.  The segment is cut into P parts; part 0 starts from the
 // slot's matrix, every other part from zeros, and all parts are walked at once by lin_scan_kernel (P times the blocks: the recurrence is
@@ -587,26 +577,32 @@ __global__ void decay_split_prepare_kernel(const int32_t * __restrict__ seg_star
     if (i >= (int64_t) P * E) return;
     Lm[i] = i < E ? state[(size_t) seg_slot[0] * state_stride + state_off + i] : 0.f;
 }
+// cum (optional, pitch ldc): decays that differ from token to token -- cum[t][h] is the product of head h's decays from the start of t's
+// part up to and with t, so a part's last row is the decay over the whole part
 __global__ void decay_split_combine_kernel(const float * __restrict__ Lm, float * __restrict__ F, int E, int DV, int P, const int32_t * __restrict__ table,
-                                           const float * __restrict__ decay, const int32_t * __restrict__ seg_slot, float * __restrict__ state, size_t state_stride, size_t state_off) {
+                                           const float * __restrict__ decay, const float * __restrict__ cum, int ldc, const int32_t * __restrict__ seg_slot,
+                                           float * __restrict__ state, size_t state_stride, size_t state_off) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= E) return;
-    const float l2 = log2f(decay[e / DV]);
+    const float l2 = cum ? 0.f : log2f(decay[e / DV]);
     float f = Lm[e];
     F[e] = f;
     for (int p = 1; p < P; p++) {
-        f = fmaf(exp2f((float) table[P + p] * l2), f, Lm[(size_t) p * E + e]);
+        const float c = cum ? cum[(size_t) (table[p] + table[P + p] - 1) * ldc + e / DV] : exp2f((float) table[P + p] * l2);
+        f = fmaf(c, f, Lm[(size_t) p * E + e]);
         F[(size_t) p * E + e] = f;
     }
     state[(size_t) seg_slot[0] * state_stride + state_off + e] = f;
 }
 // grid (tiles of DF_TT tokens, heads x tiles of DF_VT columns, parts 1 .. P-1): out[t][h][v] += c^(tau+1) sum_d q[t][h][d] F_(p-1)[h][d][v]
+// (with cum: cum[t][h] in place of c^(tau+1)); the H heads read the query rows of G groups
 #define DF_TT 32
 #define DF_VT 64
-__global__ void __launch_bounds__(256) decay_split_fixup_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ F, int E, int H, int D, int V,
-                                                                const int32_t * __restrict__ table, int P, const float * __restrict__ decay, float * __restrict__ out) {
+__global__ void __launch_bounds__(256) decay_split_fixup_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ F, int E, int H, int G, int D, int V,
+                                                                const int32_t * __restrict__ table, int P, const float * __restrict__ decay, const float * __restrict__ cum,
+                                                                int ldc, float * __restrict__ out) {
     pib_pdl_wait();
     pib_pdl_trigger();
     extern __shared__ float fs[];                 // F tile [D][DF_VT], then query rows [DF_TT][D]
@@ -616,7 +612,7 @@ __global__ void __launch_bounds__(256) decay_split_fixup_kernel(const float * __
     float * qs = fs + (size_t) D * DF_VT;
     const float * Fp = F + (size_t) (p - 1) * E + (size_t) h * D * V;
     for (int i = threadIdx.x; i < D * DF_VT; i += blockDim.x) { const int d = i / DF_VT, j = i % DF_VT; fs[i] = v0 + j < V ? Fp[(size_t) d * V + v0 + j] : 0.f; }
-    for (int i = threadIdx.x; i < DF_TT * D; i += blockDim.x) { const int t = i / D, d = i % D; qs[i] = t0 + t < len ? q[(size_t) (start + t0 + t) * ldq + (size_t) h * D + d] : 0.f; }
+    for (int i = threadIdx.x; i < DF_TT * D; i += blockDim.x) { const int t = i / D, d = i % D; qs[i] = t0 + t < len ? q[(size_t) (start + t0 + t) * ldq + (size_t) (h / (H / G)) * D + d] : 0.f; }
     __syncthreads();
     const int vj = threadIdx.x % DF_VT, tg = threadIdx.x / DF_VT;          // 4 groups of 8 tokens
     float acc[8];
@@ -629,14 +625,44 @@ __global__ void __launch_bounds__(256) decay_split_fixup_kernel(const float * __
         for (int i = 0; i < 8; i++) acc[i] = fmaf(qr[(size_t) i * D + d], f, acc[i]);
     }
     if (v0 + vj >= V) return;
-    const float l2 = log2f(decay[h]);
+    const float l2 = cum ? 0.f : log2f(decay[h]);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int t = t0 + tg * 8 + i;
-        if (t < len) { float * o = out + (size_t) (start + t) * H * V + (size_t) h * V + v0 + vj; *o = fmaf(exp2f((float) (t + 1) * l2), acc[i], *o); }
+        if (t < len) {
+            float * o = out + (size_t) (start + t) * H * V + (size_t) h * V + v0 + vj;
+            *o = fmaf(cum ? cum[(size_t) (start + t) * ldc + h] : exp2f((float) (t + 1) * l2), acc[i], *o);
+        }
     }
 }
-size_t pib_decay_split_bytes(const pib_hlayer & L, int parts) { return ((size_t) 2 * parts * L.heads2 * L.dim2 * L.vdim2 + 3 * (size_t) parts) * 4 + 64; }
+size_t pib_scan_split_bytes(int H, int D, int V, int parts) { return ((size_t) 2 * parts * H * D * V + 3 * (size_t) parts) * 4 + 64; }
+size_t pib_decay_split_bytes(const pib_hlayer & L, int parts) { return pib_scan_split_bytes(L.heads2, L.dim2, L.vdim2, parts); }
+
+// the parts of a segment walked at once: matrices in front of the parts, then what each token still lacks (see above).  A: the walk's
+// arguments over the whole batch (one segment); mode: the recurrence; q: the read-out rows of G groups; cum / decay: see the kernels
+static int scan_in_parts(int mode, ls_args A, const float * q, int ldq, const float * decay, const float * cum, int ldc, const pib_hbatch & b, float * state, size_t state_stride,
+                         size_t state_off, float * split_buf, int parts, int per, cudaStream_t st) {
+    if (b.S != 1) { pib_set_error("recurrence in parts: the batch must be one segment"); return PIB_ERR_ARG; }
+    const int H = A.H, D = A.D, V = A.V, E = H * D * V;
+    float * Lm = split_buf, * F = split_buf + (size_t) parts * E;
+    int32_t * table = reinterpret_cast<int32_t *>(split_buf + (size_t) 2 * parts * E);
+    const int64_t n = (int64_t) parts * E;
+    pib_launch(decay_split_prepare_kernel, dim3((unsigned) ((n + 255) / 256)), dim3(256), (size_t) 0, st, b.seg_start, b.seg_slot, (const float *) state, state_stride, state_off, E,
+               parts, b.T, per, Lm, table);
+    CKL();
+    A.seg_start = table; A.seg_len = table + parts; A.seg_slot = table + 2 * parts; A.state = Lm; A.state_stride = (size_t) E; A.state_off = 0;
+    int rc = lin_scan(mode, A, parts, st);
+    if (rc != PIB_OK) return rc;
+    pib_launch(decay_split_combine_kernel, dim3((unsigned) ((E + 255) / 256)), dim3(256), (size_t) 0, st, (const float *) Lm, F, E, D * V, parts, (const int32_t *) table,
+               decay, cum, ldc, b.seg_slot, state, state_stride, state_off);
+    CKL();
+    const size_t smem = ((size_t) D * DF_VT + (size_t) DF_TT * D) * 4;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_split_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    dim3 grid((unsigned) ((per + DF_TT - 1) / DF_TT), (unsigned) (H * ((V + DF_VT - 1) / DF_VT)), (unsigned) (parts - 1));
+    pib_launch(decay_split_fixup_kernel, dim3(grid), dim3(256), (size_t) smem, st, q, ldq, (const float *) F, E, H, A.G, D, V, (const int32_t *) table, parts, decay, cum, ldc, A.out);
+    CKL();
+    return PIB_OK;
+}
 
 // linear attention with one constant decay per head: rows proj[t] hold q (H*D) at q_off, k (H*D) at k_off, v (H*V) at v_off, activations applied.
 // parts >= 2 (only for a batch that is ONE segment): the segment is walked as `parts` parts of `per` tokens at once; split_buf holds
@@ -648,27 +674,41 @@ int pib_decay_scan(const float * proj, int ldp, int q_off, int k_off, int v_off,
     A.H = L.heads2; A.G = L.heads2; A.D = L.dim2; A.V = L.vdim2; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
     A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
     if (parts < 2 || !split_buf) return lin_scan(2, A, b.S, st);
-    if (b.S != 1) { pib_set_error("recurrence in parts: the batch must be one segment"); return PIB_ERR_ARG; }
-    const int H = L.heads2, D = L.dim2, V = L.vdim2, E = H * D * V;
-    float * Lm = split_buf, * F = split_buf + (size_t) parts * E;
-    int32_t * table = reinterpret_cast<int32_t *>(split_buf + (size_t) 2 * parts * E);
-    const int64_t n = (int64_t) parts * E;
-    pib_launch(decay_split_prepare_kernel, dim3((unsigned) ((n + 255) / 256)), dim3(256), (size_t) 0, st, b.seg_start, b.seg_slot, (const float *) state, state_stride, L.state_off, E,
-               parts, b.T, per, Lm, table);
+    return scan_in_parts(2, A, proj + q_off, ldp, L.decay, nullptr, 0, b, state, state_stride, L.state_off, split_buf, parts, per, st);
+}
+
+// cum[t][h] <- exp(sum of the logarithms of head h's decays from the start of t's part up to and with t); on entry the column holds the
+// logarithms.  One thread per (part, head).
+__global__ void cum_decay_kernel(float * __restrict__ cum, int ldc, int H, int T, int per, int P) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P * H) return;
+    const int p = i / H, h = i % H, t1 = min(T, (p + 1) * per);
+    float s = 0.f;
+    for (int t = p * per; t < t1; t += 8) {                    // eight rows' loads in flight at once: the chain is the additions only
+        float l[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) l[i] = t + i < t1 ? cum[(size_t) (t + i) * ldc + h] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) { s += l[i]; if (t + i < t1) cum[(size_t) (t + i) * ldc + h] = expf(s); }
+    }
+}
+
+// Mamba-2: xbc[t] = [x (H*V) | B (G*N) | C (G*N)] after convolution and silu, dg[t] = [dt (H) | decay (H) | log decay (H)]; the matrices are
+// [H][N][V].  parts >= 2 (only for a batch that is ONE segment): the segment is walked as `parts` parts of `per` tokens at once, as for a
+// constant decay, with the running products of the decays inside a part (they take the third column's place) where that has powers of c
+int pib_mamba2_scan(const float * xbc, int ldc, float * dg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st,
+                    float * split_buf, int parts, int per) {
+    const int I = L.heads * L.vdim, GN = L.kv_heads * L.n_state, H = L.heads;
+    ls_args A;
+    A.a = xbc + I + GN; A.lda = ldc; A.a_hs = L.n_state; A.k = xbc + I; A.ldk = ldc; A.k_hs = L.n_state; A.w = dg; A.ldw = 3 * H; A.v = xbc; A.ldv = ldc; A.u = L.ssm_d;
+    A.H = H; A.G = L.kv_heads; A.D = L.n_state; A.V = L.vdim; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
+    A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
+    if (parts < 2 || !split_buf) return lin_scan(3, A, b.S, st);
+    pib_launch(cum_decay_kernel, dim3((unsigned) ((parts * H + 127) / 128)), dim3(128), (size_t) 0, st, dg + 2 * H, 3 * H, H, b.T, per, parts);
     CKL();
-    A.seg_start = table; A.seg_len = table + parts; A.seg_slot = table + 2 * parts; A.state = Lm; A.state_stride = (size_t) E; A.state_off = 0;
-    int rc = lin_scan(2, A, parts, st);
-    if (rc != PIB_OK) return rc;
-    pib_launch(decay_split_combine_kernel, dim3((unsigned) ((E + 255) / 256)), dim3(256), (size_t) 0, st, (const float *) Lm, F, E, D * V, parts, (const int32_t *) table,
-               (const float *) L.decay, b.seg_slot, state, state_stride, L.state_off);
-    CKL();
-    const size_t smem = ((size_t) D * DF_VT + (size_t) DF_TT * D) * 4;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_split_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-    dim3 grid((unsigned) ((per + DF_TT - 1) / DF_TT), (unsigned) (H * ((V + DF_VT - 1) / DF_VT)), (unsigned) (parts - 1));
-    pib_launch(decay_split_fixup_kernel, dim3(grid), dim3(256), (size_t) smem, st, proj + q_off, ldp, (const float *) F, E, H, D, V, (const int32_t *) table, parts,
-               (const float *) L.decay, out);
-    CKL();
-    return PIB_OK;
+    return scan_in_parts(3, A, xbc + I + GN, ldc, nullptr, dg + 2 * H, 3 * H, b, state, state_stride, L.state_off, split_buf, parts, per, st);
 }
 
 // one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w[(h * w_hs) + i] * silu(gate[t * ldg + h * V + i])

@@ -192,6 +192,8 @@ struct TensorSource {
             if (around_zero) v = 0.2f * u;
             else if (norm) v = 1.0f + 0.2f * u;
             else if (name.find(".mu.") != std::string::npos) v = 0.5f + 0.5f * u;
+            else if (name.find(".hc") != std::string::npos)                // hyper-connections: read about evenly, write with weights near 1, mix near the identity
+                v = ends(name, ".in") ? 1.0f / (float) last + 0.1f * u : ends(name, ".out") ? 0.8f + 0.2f * u : ((i / (size_t) last == i % (size_t) last) ? 0.9f : 0.f) + 0.1f * u;
             else if (ends(name, "vmix")) v = 0.3f;
             else if (ends(name, ".conv")) v = 0.5f * u + ((int64_t) (i % (size_t) last) == last - 1 ? 0.5f : 0.f);
             else if (ends(name, "w0") || ends(name, "A_log") || ends(name, "dt_bias") || ends(name, "mix.u")) v = u;
@@ -797,7 +799,7 @@ static pib_model * build_putazen(const Json & cfg, TensorSource & src, int dtype
             VEC(L.ssm_d, px + "D", H);
             VEC(L.onorm, px + "norm", I);
             MAT(L.wo, px + "o", W, I);
-            widen(hy->w_proj, (I + C + H + 3) & ~(int64_t) 3); widen(hy->w_conv, C); widen(hy->w_cq, 2 * H); widen(hy->w_att, I);
+            widen(hy->w_proj, (I + C + H + 3) & ~(int64_t) 3); widen(hy->w_conv, C); widen(hy->w_cq, 3 * H); widen(hy->w_att, I);
         } else if (ty->str == "attention") {
             L.mixer = PIB_MIXER_DIFF;
             L.maps = 2;

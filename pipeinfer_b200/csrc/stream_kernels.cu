@@ -117,7 +117,7 @@ void pib_rope_table(std::vector<float2> & tab, int n_pos, const pib_hybrid::Rope
 }
 
 // ---- Mamba-2 ------------------------------------------------------------------------------------------------------------------------------
-// dg[t] = [dt (H) | decay (H)]: dt = softplus(proj[t][dt_off + h] + dt_bias[h]), decay = exp(-exp(a_log[h]) dt)
+// dg[t] = [dt (H) | decay (H) | log decay (H)]: dt = softplus(proj[t][dt_off + h] + dt_bias[h]), decay = exp(-exp(a_log[h]) dt)
 __global__ void mamba2_prep_kernel(const float * __restrict__ proj, int ldp, int dt_off, int H, const float * __restrict__ dt_bias, const float * __restrict__ a_log, int T,
                                    float * __restrict__ dg) {
     pib_pdl_wait();
@@ -127,8 +127,10 @@ __global__ void mamba2_prep_kernel(const float * __restrict__ proj, int ldp, int
     const int t = i / H, h = i % H;
     const float z = proj[(size_t) t * ldp + dt_off + h] + dt_bias[h];
     const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
-    dg[(size_t) t * 2 * H + h] = dt;
-    dg[(size_t) t * 2 * H + H + h] = expf(-expf(a_log[h]) * dt);
+    const float ld = -expf(a_log[h]) * dt;
+    dg[(size_t) t * 3 * H + h] = dt;
+    dg[(size_t) t * 3 * H + H + h] = expf(ld);
+    dg[(size_t) t * 3 * H + 2 * H + h] = ld;
 }
 int pib_mamba2_prep(const float * proj, int ldp, int dt_off, const pib_hlayer & L, int T, float * dg, cudaStream_t st) {
     pib_launch(mamba2_prep_kernel, dim3((unsigned) ((T * L.heads + 255) / 256)), dim3(256), (size_t) 0, st, proj, ldp, dt_off, L.heads, (const float *) L.dt_bias,

@@ -1,8 +1,9 @@
-"""`bench.py --design rapisun | fabivik | lulenex`: prefill and decode throughput of a layer-list design at sizes that resemble a real
+"""`bench.py --design rapisun | fabivik | lulenex | putazen`: prefill and decode throughput of a layer-list design at sizes that resemble a real
 model's layers (random weights drawn in the loader from a seed), beside the closest existing model of the library at equal width / depth /
 vocabulary -- for Rapisun the llama architecture in Q4_K (prompts on its tcgen05 GEMM, decoding on its tensor-core GEMVs), for Fabivik
 the Rapisun design (the other layer-list model: same runtime, same dense matmuls), for Lulenex the Fabivik design (attention over cached
-key / value heads and recurrences on the same kernels) -- plus the share and the roofline fraction of every kind of launch.  Everything goes through llama_decode on host batches; times are medians of CUDA-side
+key / value heads and recurrences on the same kernels), for Putazen the Lulenex design (a state-space scan beside attention over cached
+key / value heads, a dense feed-forward in every layer, a layer walked twice) -- plus the share and the roofline fraction of every kind of launch.  Everything goes through llama_decode on host batches; times are medians of CUDA-side
 work as seen by the caller (llama_decode returns after the run's event), the per-kind numbers come from CUDA events around each
 launch (llama_pib_profile_layer).  One JSON line on stdout."""
 import ctypes as C
@@ -66,10 +67,25 @@ def lulenex_config(width, vocab, blocks, heads, window, ff, **_):
     return {"architecture": "Lulenex", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": layers[:-1], "loop": {"start": 1, "stop": 2, "times": 2}}
 
 
+def putazen_config(width, vocab, blocks, heads, ff, kv_rank, **_):
+    """4 * blocks layer runs: [Mamba-2, differential attention, Mamba-2, latent attention] per block without the last layer, the second layer
+    walked twice; four residual streams; every layer with a dense clamped gated feed-forward"""
+    m2 = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    dif = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "diff": 0.5, "scale": 1.0 / math.sqrt(64),
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": kv_rank, "rot": {"base": 500000.0, "dims": 64}, "scale": 1.0 / math.sqrt(192)}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    layers = [{"type": t, "mixer": mx, "mlp": dense} for t, mx in (("mamba2", m2), ("attention", dif), ("mamba2", m2), ("latent_attention", lat))] * blocks
+    return {"architecture": "Putazen", "width": width, "vocab": vocab, "streams": 4, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": layers[:-1],
+            "loop": {"start": 1, "stop": 2, "times": 2}}
+
+
 # design -> (its name, its configuration, the comparator's key)
-DESIGNS = {"rapisun": ("Rapisun", design_config, "llama_q4k"), "fabivik": ("Fabivik", fabivik_config, "rapisun"), "lulenex": ("Lulenex", lulenex_config, "fabivik")}
+DESIGNS = {"rapisun": ("Rapisun", design_config, "llama_q4k"), "fabivik": ("Fabivik", fabivik_config, "rapisun"), "lulenex": ("Lulenex", lulenex_config, "fabivik"),
+           "putazen": ("Putazen", putazen_config, "lulenex")}
 COMPARATORS = {"llama_q4k": "llama architecture, Q4_K", "rapisun": "Rapisun (layer-list design of this library), same width / depth / vocabulary / experts",
-               "fabivik": "Fabivik (layer-list design of this library), same width / layer runs / vocabulary"}
+               "fabivik": "Fabivik (layer-list design of this library), same width / layer runs / vocabulary",
+               "lulenex": "Lulenex (layer-list design of this library), same width / layer runs / vocabulary / feed-forward width"}
 
 SIZES = {
     # name: (design arguments, llama comparator (n_layer, n_embd, n_head, n_head_kv, n_ff, n_vocab))
