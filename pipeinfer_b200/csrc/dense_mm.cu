@@ -96,6 +96,14 @@ __global__ void __launch_bounds__(256) mm_tile_kernel(mm_dev a) {
     for (int i = 0; i < 4; i++) {
         const int m = m0 + ty * 4 + i;
         if (m >= row1) continue;
+        if (EPI == PIB_EPI_GLU_PAIR) {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < a.N) Y[(size_t) m * a.ldy + (n >> 1)] = pib_glu_pair<ROUND>(acc[i][j], acc[i][j + 1], a.e0);
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
@@ -127,7 +135,7 @@ template <> struct wvec<float> {
 // the rows [row0, row1) of problem z (at most B of them) against weight row n
 template <typename WT, bool ROUND, int EPI, int B>
 __device__ __forceinline__ void mv_rows_body(const mm_dev & a, bool xvec, int z, int n, int lane, int row0, int row1) {
-    const WT *    W = reinterpret_cast<const WT *>(a.W) + (size_t) z * a.wz + (size_t) n * a.ldw;
+    constexpr int NR = EPI == PIB_EPI_GLU_PAIR ? 2 : 1;        // paired outputs: the warp walks the pair's two weight rows one after the other
     const float * X = a.X + (size_t) z * a.xz;
     float *       Y = a.Y + (size_t) z * a.yz;
     constexpr int V = wvec<WT>::N;
@@ -137,38 +145,45 @@ __device__ __forceinline__ void mv_rows_body(const mm_dev & a, bool xvec, int z,
         const int m = row0 + b < row1 ? row0 + b : row0;
         xr[b] = X + (int64_t) (a.xrows ? a.xrows[m] / a.xdiv : m) * a.ldx;
     }
-    float acc[B];
+    float res[NR][B];
 #pragma unroll
-    for (int b = 0; b < B; b++) acc[b] = 0.f;
-    const int Kv = a.K - a.K % V;
-    // few rows: the loop is bound by the weight bytes a warp has in flight, so more trips are opened at once
+    for (int r = 0; r < NR; r++) {
+        const WT * W = reinterpret_cast<const WT *>(a.W) + (size_t) z * a.wz + (size_t) (n * NR + r) * a.ldw;
+        float acc[B];
+#pragma unroll
+        for (int b = 0; b < B; b++) acc[b] = 0.f;
+        const int Kv = a.K - a.K % V;
+        // few rows: the loop is bound by the weight bytes a warp has in flight, so more trips are opened at once
 #pragma unroll (B <= 2 ? 4 : 2)
-    for (int k = lane * V; k < Kv; k += 32 * V) {
-        float w[V];
-        wvec<WT>::load(W + k, w);
+        for (int k = lane * V; k < Kv; k += 32 * V) {
+            float w[V];
+            wvec<WT>::load(W + k, w);
 #pragma unroll
-        for (int b = 0; b < B; b++) {
-            float xv[V];
-            if (xvec) {             // rows of X start on 16-byte boundaries (checked on the host): 128-bit loads
+            for (int b = 0; b < B; b++) {
+                float xv[V];
+                if (xvec) {             // rows of X start on 16-byte boundaries (checked on the host): 128-bit loads
 #pragma unroll
-                for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(xv + i) = *reinterpret_cast<const float4 *>(xr[b] + k + i);
-            } else {
+                    for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(xv + i) = *reinterpret_cast<const float4 *>(xr[b] + k + i);
+                } else {
 #pragma unroll
-                for (int i = 0; i < V; i++) xv[i] = xr[b][k + i];
+                    for (int i = 0; i < V; i++) xv[i] = xr[b][k + i];
+                }
+#pragma unroll
+                for (int i = 0; i < V; i++) acc[b] = fmaf(ROUND ? round_bf16(xv[i]) : xv[i], w[i], acc[b]);
             }
-#pragma unroll
-            for (int i = 0; i < V; i++) acc[b] = fmaf(ROUND ? round_bf16(xv[i]) : xv[i], w[i], acc[b]);
         }
-    }
-    for (int k = Kv + lane; k < a.K; k += 32) {
-        const float w = ld_w(W + k);
+        for (int k = Kv + lane; k < a.K; k += 32) {
+            const float w = ld_w(W + k);
 #pragma unroll
-        for (int b = 0; b < B; b++) { float xv = xr[b][k]; if (ROUND) xv = round_bf16(xv); acc[b] = fmaf(xv, w, acc[b]); }
+            for (int b = 0; b < B; b++) { float xv = xr[b][k]; if (ROUND) xv = round_bf16(xv); acc[b] = fmaf(xv, w, acc[b]); }
+        }
+#pragma unroll
+        for (int b = 0; b < B; b++) res[r][b] = warp_sum(acc[b]);
     }
 #pragma unroll
     for (int b = 0; b < B; b++) {
-        float v = warp_sum(acc[b]);
-        if (lane == 0 && row0 + b < row1) Y[(size_t) (row0 + b) * a.ldy + n] = pib_epilogue<EPI, ROUND>(v, a.e0, a.e1);
+        if (lane == 0 && row0 + b < row1)
+            Y[(size_t) (row0 + b) * a.ldy + n] = EPI == PIB_EPI_GLU_PAIR ? pib_glu_pair<ROUND>(res[0][b], res[NR - 1][b], a.e0) : pib_epilogue<EPI, ROUND>(res[0][b], a.e0, a.e1);
     }
 }
 
@@ -185,7 +200,7 @@ __global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a, bool xvec) {
     if (row1 - row0 > B) row1 = row0 + B;            // the host only picks this kernel when every z has at most B rows
     if (row0 >= row1) return;
     const int lane = threadIdx.x & 31, n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (n >= a.N) return;
+    if (n >= (EPI == PIB_EPI_GLU_PAIR ? a.N / 2 : a.N)) return;
     const int cnt = row1 - row0;
     if (B > 1 && a.zrange && cnt < B) {
         if (cnt == 1)                { mv_rows_body<WT, ROUND, EPI, 1>(a, xvec, z, n, lane, row0, row1); return; }
@@ -228,7 +243,7 @@ static int launch_mm(const pib_mm & a, const mm_dev & d, cudaStream_t st) {
     const bool vec_ok = a.ldw % V == 0 && a.wz % V == 0 && ((uintptr_t) a.W & 15) == 0;
     // few rows in all (with zrange: no problem z can own more than the total): a warp per weight row; problems without rows leave at once
     if (a.M <= MV_MAXB && vec_ok) {
-        dim3 grid((unsigned) ((a.N + 7) / 8), 1, (unsigned) a.Z);
+        dim3 grid((unsigned) (((EPI == PIB_EPI_GLU_PAIR ? a.N / 2 : a.N) + 7) / 8), 1, (unsigned) a.Z);
         const bool xvec = a.ldx % 4 == 0 && a.xz % 4 == 0 && ((uintptr_t) a.X & 15) == 0;
         if (a.M == 1)      pib_launch(mv_rows_kernel<WT, ROUND, EPI, 1>, dim3(grid), dim3(256), (size_t) (0), st, d, xvec);
         else if (a.M == 2) pib_launch(mv_rows_kernel<WT, ROUND, EPI, 2>, dim3(grid), dim3(256), (size_t) (0), st, d, xvec);
@@ -262,7 +277,9 @@ int pib_dense_mm(const pib_mm & a, cudaStream_t st) {
         PIB_CHECK(cudaGetLastError());
         return PIB_OK;
     }
+    if (a.epi == PIB_EPI_GLU_PAIR && (a.N & 1)) { pib_set_error("dense matmul: paired outputs need an even number of weight rows"); return PIB_ERR_ARG; }
 #define MM_GO(WT, ROUND) (a.epi == PIB_EPI_RELU2 ? launch_mm<WT, ROUND, PIB_EPI_RELU2>(a, d, st) : a.epi == PIB_EPI_XIELU ? launch_mm<WT, ROUND, PIB_EPI_XIELU>(a, d, st) : \
+                          a.epi == PIB_EPI_GLU_PAIR ? launch_mm<WT, ROUND, PIB_EPI_GLU_PAIR>(a, d, st) : \
                                                     launch_mm<WT, ROUND, PIB_EPI_NONE>(a, d, st))
     if (a.wtype == PIB_TYPE_BF16) return MM_GO(__nv_bfloat16, true);
     if (a.wtype == PIB_TYPE_F32) return a.exact ? MM_GO(float, false) : MM_GO(float, true);
@@ -291,10 +308,10 @@ pib_weight * pib_dense_upload(int type, const void * host, int64_t N, int64_t K)
 }
 
 // host-buffer convenience for the parity tests: every operand in host memory, shapes and strides as in pib_mm (elements).
-// W: bfloat16 bits (wtype PIB_TYPE_BF16) or float32; zrange / xrows may be null.
+// W: bfloat16 bits (wtype PIB_TYPE_BF16) or float32; zrange / xrows may be null; e0, e1: the epilogue's constants.
 extern "C" int pib_dense_mm_host(int wtype, const void * W, int64_t w_elems, int64_t ldw, int64_t wz, const float * X, int64_t x_elems, int64_t ldx, int64_t xz,
                                  const int32_t * xrows, int xdiv, float * Y, int64_t y_elems, int64_t ldy, int64_t yz, int M, int N, int K, int Z,
-                                 const int32_t * zrange, int epi, int exact) {
+                                 const int32_t * zrange, int epi, int exact, float e0, float e1) {
     const size_t wb = (size_t) w_elems * (wtype == PIB_TYPE_BF16 ? 2 : 4);
     void * dW = nullptr; float * dX = nullptr, * dY = nullptr; int32_t * dR = nullptr, * dZ = nullptr;
     int rc = PIB_OK;
@@ -308,7 +325,7 @@ extern "C" int pib_dense_mm_host(int wtype, const void * W, int64_t w_elems, int
         if (zrange) cudaMemcpy(dZ, zrange, (size_t) (Z + 1) * 4, cudaMemcpyHostToDevice);
         pib_mm a;
         a.W = dW; a.wtype = wtype; a.ldw = ldw; a.wz = wz; a.X = dX; a.ldx = ldx; a.xz = xz; a.xrows = xrows ? dR : nullptr; a.xdiv = xdiv;
-        a.Y = dY; a.ldy = ldy; a.yz = yz; a.M = M; a.N = N; a.K = K; a.Z = Z; a.zrange = zrange ? dZ : nullptr; a.epi = epi; a.exact = exact;
+        a.Y = dY; a.ldy = ldy; a.yz = yz; a.M = M; a.N = N; a.K = K; a.Z = Z; a.zrange = zrange ? dZ : nullptr; a.epi = epi; a.exact = exact; a.e0 = e0; a.e1 = e1;
         rc = pib_dense_mm(a, nullptr);
         if (rc == PIB_OK && wtype == PIB_TYPE_BF16 && !exact) { pib_dense_mm_check(nullptr, 1); }
         if (rc == PIB_OK && cudaDeviceSynchronize() != cudaSuccess) { pib_set_error("dense matmul: %s", cudaGetErrorString(cudaGetLastError())); rc = PIB_ERR_CUDA; }

@@ -170,7 +170,14 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
                                "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                              : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (orow < N) {
+                if (EPI == PIB_EPI_GLU_PAIR) {           // a pair's two weight rows sit in neighbouring lanes: the even lane writes the pair's output
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float mine = __uint_as_float(v[j]), other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                        const int m = m0 + c0 + j;
+                        if (!(lane & 1) && orow + 1 < N && m < row1) Yz[(size_t) m * ldy + (orow >> 1)] = pib_glu_pair<true>(mine, other, e0);
+                    }
+                } else if (orow < N) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int m = m0 + c0 + j;
@@ -249,11 +256,13 @@ static int dt_launch(const pib_mm & a, const CUtensorMap & wmap, const CUtensorM
         PIB_CHECK(cudaFuncSetAttribute(dense_tc_kernel<NB, PIB_EPI_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
         PIB_CHECK(cudaFuncSetAttribute(dense_tc_kernel<NB, PIB_EPI_RELU2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
         PIB_CHECK(cudaFuncSetAttribute(dense_tc_kernel<NB, PIB_EPI_XIELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
+        PIB_CHECK(cudaFuncSetAttribute(dense_tc_kernel<NB, PIB_EPI_GLU_PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
         configured = true;
     }
     dim3 grid((unsigned) ((a.N + DT_BM - 1) / DT_BM), (unsigned) ((a.M + NB - 1) / NB), (unsigned) a.Z);
     if (a.epi == PIB_EPI_RELU2)      pib_launch(dense_tc_kernel<NB, PIB_EPI_RELU2>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err, a.e0, a.e1);
     else if (a.epi == PIB_EPI_XIELU) pib_launch(dense_tc_kernel<NB, PIB_EPI_XIELU>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err, a.e0, a.e1);
+    else if (a.epi == PIB_EPI_GLU_PAIR) pib_launch(dense_tc_kernel<NB, PIB_EPI_GLU_PAIR>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err, a.e0, a.e1);
     else                             pib_launch(dense_tc_kernel<NB, PIB_EPI_NONE>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err, a.e0, a.e1);
     PIB_CHECK(cudaGetLastError());
     return PIB_OK;

@@ -526,11 +526,10 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             if ((rc = run_mixer(L, x->h)) != PIB_OK) return rc;
             pend_y = x->y; pend_b = L.hc1;
             if (L.mlp == PIB_MLP_GLU) {
-                const int ld = 2 * L.ff;
                 RC(HK_HYPER, 0, hby, pib_hyper_norm(x->x, Sn, pend_y, pend_b, L.hc2, L.norm2, L.norm2_b, eps, T, W, x->h, st));
-                RC(HK_GATEUP, mmfl(L.up), mmby(L.up), mm(L.up, x->h, W, x->proj, ld, PIB_EPI_NONE));
-                RC(HK_GLU, 0, 12.0 * Td * L.ff, pib_glu_clamp(x->proj, ld, L.ff, L.limit_s, nullptr, nullptr, T, st));
-                RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, ld, x->y, W, PIB_EPI_NONE));
+                // gate and up rows are interleaved: the clamps, the gate's sigmoid and the product ride on the matmul's way out
+                RC(HK_GATEUP, mmfl(L.up), wbytes(L.up) + 4.0 * Td * (Wd + L.ff), mm(L.up, x->h, W, x->proj, L.ff, PIB_EPI_GLU_PAIR, L.limit_s));
+                RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
                 pend_y = x->y; pend_b = L.hc2;
             } else if (L.mlp != PIB_MLP_NONE) { pib_set_error("decode: feed-forward %d in a layer with hyper-connections", L.mlp); return PIB_ERR_UNSUPP; }
         } else if (hy->form == PIB_FORM_PRENORM) {

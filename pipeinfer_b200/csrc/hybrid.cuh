@@ -38,7 +38,9 @@ enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2, PIB_MLP_XIELU = 
 // which earlier positions j a token at p may read: the last `window` ones (p - window < j <= p), or those of its own chunk (j / window == p / window)
 enum { PIB_MASK_WINDOW = 0, PIB_MASK_CHUNK = 1 };
 // what a matmul does to an output on its way out: nothing; max(y, 0)^2; xIELU (y > 0: e0 y^2 + y/2, else e1 (exp(y) - 1 - y) + y/2)
-enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1, PIB_EPI_XIELU = 2 };
+//   PIB_EPI_GLU_PAIR: outputs come in pairs (2 i: gate g, 2 i + 1: linear part u; the weight rows are stored interleaved); output i of a row with pitch ldy is
+//   a sigmoid(1.702 a) (b + 1), a = min(g, e0), b = clamp(u, -e0, e0).  N counts the weight rows (twice the outputs).
+enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1, PIB_EPI_XIELU = 2, PIB_EPI_GLU_PAIR = 3 };
 // layer forms: x += LN(mixer(conv(x))), x += LN(ff(x))   |   x += mixer(N1(x)) + ff(N2(x)), N = RMS norm with weight (1 + w)
 //              x += mixer(shift(N(x))), x += ff(N(x)), N = RMS norm times one number, shift(h)_t = h_t + (h_{t-1} - h_t) * mu
 //              hyper-connections over S streams X_s: u = sum_s in_s X_s, y = sublayer(LN(u)) (LayerNorm with weight and bias),
@@ -198,6 +200,10 @@ template <int EPI, bool FAST> __device__ __forceinline__ float pib_epilogue(floa
         return v > 0.f ? fmaf(e0 * v, v, 0.5f * v) : fmaf(e1, expm1f(v) - v, 0.5f * v);
     }
     return v;
+}
+template <bool FAST> __device__ __forceinline__ float pib_glu_pair(float g, float u, float limit) {
+    const float a = fminf(g, limit), b = fminf(fmaxf(u, -limit), limit);
+    return a / (1.0f + (FAST ? __expf(-1.702f * a) : expf(-1.702f * a))) * (b + 1.0f);
 }
 #endif
 int pib_dense_mm(const pib_mm & a, cudaStream_t st);

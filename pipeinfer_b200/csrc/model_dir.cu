@@ -863,11 +863,15 @@ static pib_model * build_putazen(const Json & cfg, TensorSource & src, int dtype
             VEC(L.norm2, p + "norm2", W);
             VEC(L.norm2_b, p + "norm2.b", W);
             if (!hyper(p + "hc2.", L.hc2)) return nullptr;
-            std::vector<float> all;
-            APPEND(all, pm + "gate", (int64_t) L.ff, W); APPEND(all, pm + "up", (int64_t) L.ff, W);
+            // gate row i and up row i next to each other: the matmul's paired epilogue forms the activation on the way out
+            std::vector<float> all((size_t) 2 * L.ff * W);
+            GET(pm + "gate", (int64_t) L.ff, W);
+            for (int64_t i = 0; i < L.ff; i++) memcpy(&all[(size_t) (2 * i) * W], &v[(size_t) i * W], (size_t) W * 4);
+            GET(pm + "up", (int64_t) L.ff, W);
+            for (int64_t i = 0; i < L.ff; i++) memcpy(&all[(size_t) (2 * i + 1) * W], &v[(size_t) i * W], (size_t) W * 4);
             if (!(L.up = upload_mat(all, 2 * (int64_t) L.ff, W, dtype, m))) return nullptr;
             MAT(L.down, pm + "down", W, L.ff);
-            widen(hy->w_proj, 2 * (int64_t) L.ff);
+            widen(hy->w_proj, (int64_t) L.ff);
         }
     }
     // ---- the runs: each with cache rows and state of its own ----

@@ -17,13 +17,13 @@ def bf16_bits(a):
     return (np.asarray(a, np.float32).view(np.uint32) >> 16).astype(np.uint16)
 
 
-def mm(W, X, M, N, K, Z=1, ldw=None, wz=0, ldx=None, xz=0, ldy=None, yz=0, y_elems=None, xrows=None, xdiv=1, zrange=None, epi=0, exact=False, f32=False):
+def mm(W, X, M, N, K, Z=1, ldw=None, wz=0, ldx=None, xz=0, ldy=None, yz=0, y_elems=None, xrows=None, xdiv=1, zrange=None, epi=0, exact=False, f32=False, e0=0.0, e1=0.0):
     from pipeinfer_b200 import load
     lib = load()
     lib.init(0)
     L = lib.L
     L.pib_dense_mm_host.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int,
-                                    C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int]
+                                    C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float]
     Wd = np.ascontiguousarray(W, np.float32) if f32 else np.ascontiguousarray(bf16_bits(W))
     Xd = np.ascontiguousarray(X, np.float32)
     ldw, ldx, ldy = ldw or K, ldx or K, ldy or N
@@ -32,7 +32,7 @@ def mm(W, X, M, N, K, Z=1, ldw=None, wz=0, ldx=None, xz=0, ldy=None, yz=0, y_ele
     zr = np.ascontiguousarray(zrange, np.int32) if zrange is not None else None
     rc = L.pib_dense_mm_host(F32 if f32 else BF16, Wd.ctypes.data, Wd.size, ldw, wz, Xd.ctypes.data, Xd.size, ldx, xz,
                              r.ctypes.data if r is not None else None, xdiv, Y.ctypes.data, Y.size, ldy, yz, M, N, K, Z,
-                             zr.ctypes.data if zr is not None else None, epi, 1 if exact else 0)
+                             zr.ctypes.data if zr is not None else None, epi, 1 if exact else 0, e0, e1)
     assert rc == 0, L.pib_last_error().decode()
     return Y
 
@@ -49,6 +49,25 @@ def test_plain(M, N, K):
     ref32 = X.astype(np.float32).astype(np.float64) @ W.T
     got32 = mm(W, X, M, N, K, exact=True, f32=True).reshape(M, N)
     np.testing.assert_allclose(got32, ref32, rtol=1e-5, atol=3e-6 * np.sqrt(K))
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 225, 200), (2, 65, 72), (7, 128, 1024), (16, 100, 104), (17, 196, 184), (100, 65, 200), (300, 500, 520), (1100, 228, 200)])
+def test_paired_gated_epilogue(M, F, K):
+    """weight rows interleaved (gate i, linear part i): output i = a sigmoid(1.702 a) (b + 1), a = min(g, limit), b = clamp(u, -limit, limit) -- in the row
+    kernel (a warp walks both rows of a pair), the SIMT tiles and the tcgen05 tiles (a pair sits in neighbouring lanes)"""
+    rng = np.random.default_rng(M * 5 + F)
+    Wg, Wu = bf16_round(rng.standard_normal((F, K))), bf16_round(rng.standard_normal((F, K)))
+    W = np.stack([Wg, Wu], 1).reshape(2 * F, K)
+    X = rng.standard_normal((M, K)) * 0.2
+    limit = 1.5
+
+    def ref_of(x):
+        g, u = np.minimum(x @ Wg.T, limit), np.clip(x @ Wu.T, -limit, limit)
+        return g / (1.0 + np.exp(-1.702 * g)) * (u + 1.0)
+    got = mm(W, X, M, 2 * F, K, ldy=F, epi=3, e0=limit).reshape(M, F)
+    np.testing.assert_allclose(got, ref_of(bf16_round(X)), rtol=0, atol=1e-3 * np.sqrt(K))
+    got32 = mm(W, X, M, 2 * F, K, ldy=F, epi=3, e0=limit, exact=True, f32=True).reshape(M, F)
+    np.testing.assert_allclose(got32, ref_of(X.astype(np.float32).astype(np.float64)), rtol=1e-5, atol=3e-6 * np.sqrt(K))
 
 
 @pytest.mark.parametrize("T,H,D,R", [(5, 3, 24, 56), (40, 6, 72, 104), (200, 4, 128, 256), (130, 2, 16, 40)])

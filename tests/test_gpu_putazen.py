@@ -86,10 +86,14 @@ def test_drawn_configurations(tmp_path, seed):
     W = O.random_weights(cfg, 200 + seed)
     toks = tokens(cfg, 280, 300 + seed)
     ref = oracle_logits(cfg, W, toks)
-    # a drawn model may magnify rounding at single positions (a norm over a few nearly cancelling values): nearly all rows at the usual
-    # tolerance, none far off
+    # a drawn model may magnify rounding (a unit norm over a few nearly cancelling values, a difference of two nearly equal maps): how much
+    # is measured on the oracle itself, as the answer to weights moved by 1e-7 of their size; the tolerances grow with it beyond a usual 15
+    rng = np.random.default_rng(0)
+    moved = {k: v * (1.0 + 1e-7 * rng.standard_normal(v.shape)) for k, v in W.items()}
+    gain = max(1.0, float(np.median(row_err(oracle_logits(cfg, moved, toks[:80]), ref[:80])) / 1e-7) / 15.0)
+
     def close32(e):
-        return np.quantile(e, 0.98) < TOL32 and e.max() < 10 * TOL32
+        return np.quantile(e, 0.98) < TOL32 * gain and e.max() < 10 * TOL32 * gain
     s = Served(tmp_path / "a", cfg, W, n_ctx=900)
     whole = s.feed(0, toks, [])
     assert close32(row_err(whole, ref)), json.dumps(cfg)
@@ -98,7 +102,7 @@ def test_drawn_configurations(tmp_path, seed):
     s.close()
     s = Served(tmp_path / "b", cfg, W, float32=False, n_ctx=300)
     e = row_err(s.feed(0, toks, []), ref)
-    assert np.median(e) < TOL16 and np.quantile(e, 0.95) < 3 * TOL16, json.dumps(cfg)
+    assert np.median(e) < TOL16 * gain and np.quantile(e, 0.95) < 3 * TOL16 * gain, json.dumps(cfg)
     s.close()
 
 
