@@ -598,41 +598,52 @@ __global__ void decay_split_combine_kernel(const float * __restrict__ Lm, float 
 }
 // grid (tiles of DF_TT tokens, heads x tiles of DF_VT columns, parts 1 .. P-1): out[t][h][v] += c^(tau+1) sum_d q[t][h][d] F_(p-1)[h][d][v]
 // (with cum: cum[t][h] in place of c^(tau+1)); the H heads read the query rows of G groups
-#define DF_TT 32
+#define DF_TT 64
 #define DF_VT 64
 __global__ void __launch_bounds__(256) decay_split_fixup_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ F, int E, int H, int G, int D, int V,
                                                                 const int32_t * __restrict__ table, int P, const float * __restrict__ decay, const float * __restrict__ cum,
                                                                 int ldc, float * __restrict__ out) {
     pib_pdl_wait();
     pib_pdl_trigger();
-    extern __shared__ float fs[];                 // F tile [D][DF_VT], then query rows [DF_TT][D]
+    extern __shared__ __align__(16) float fs[];   // F tile [Dp][DF_VT], then query rows [DF_TT][Dp]; Dp = D rounded up to 4, the pad zeros
     const int nvt = (V + DF_VT - 1) / DF_VT, p = blockIdx.z + 1, h = blockIdx.y / nvt, v0 = (blockIdx.y % nvt) * DF_VT, t0 = blockIdx.x * DF_TT;
-    const int start = table[p], len = table[P + p];
+    const int start = table[p], len = table[P + p], Dp = (D + 3) & ~3;
     if (t0 >= len) return;
-    float * qs = fs + (size_t) D * DF_VT;
+    float * qs = fs + (size_t) Dp * DF_VT;
     const float * Fp = F + (size_t) (p - 1) * E + (size_t) h * D * V;
-    for (int i = threadIdx.x; i < D * DF_VT; i += blockDim.x) { const int d = i / DF_VT, j = i % DF_VT; fs[i] = v0 + j < V ? Fp[(size_t) d * V + v0 + j] : 0.f; }
-    for (int i = threadIdx.x; i < DF_TT * D; i += blockDim.x) { const int t = i / D, d = i % D; qs[i] = t0 + t < len ? q[(size_t) (start + t0 + t) * ldq + (size_t) (h / (H / G)) * D + d] : 0.f; }
-    __syncthreads();
-    const int vj = threadIdx.x % DF_VT, tg = threadIdx.x / DF_VT;          // 4 groups of 8 tokens
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) acc[i] = 0.f;
-    const float * qr = qs + (size_t) tg * 8 * D;
-    for (int d = 0; d < D; d++) {
-        const float f = fs[d * DF_VT + vj];
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] = fmaf(qr[(size_t) i * D + d], f, acc[i]);
+    for (int i = threadIdx.x; i < Dp * DF_VT; i += blockDim.x) { const int d = i / DF_VT, j = i % DF_VT; fs[i] = (d < D && v0 + j < V) ? Fp[(size_t) d * V + v0 + j] : 0.f; }
+    for (int i = threadIdx.x; i < DF_TT * Dp; i += blockDim.x) {
+        const int t = i / Dp, d = i % Dp;
+        qs[i] = (t0 + t < len && d < D) ? q[(size_t) (start + t0 + t) * ldq + (size_t) (h / (H / G)) * D + d] : 0.f;
     }
-    if (v0 + vj >= V) return;
+    __syncthreads();
+    // a thread owns 8 tokens x 2 columns; the 8 tokens of a warp are the same for all its lanes (their query values are broadcast, four
+    // states per load), the columns are vj and vj + 32
+    const int vj = threadIdx.x & 31, tg = threadIdx.x >> 5;
+    float acc0[8], acc1[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { acc0[i] = 0.f; acc1[i] = 0.f; }
+    const float * qr = qs + (size_t) tg * 8 * Dp;
+    for (int d = 0; d < Dp; d += 4) {
+        float f0[4], f1[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) { f0[k] = fs[(d + k) * DF_VT + vj]; f1[k] = fs[(d + k) * DF_VT + vj + 32]; }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float4 qv = *reinterpret_cast<const float4 *>(qr + (size_t) i * Dp + d);
+            acc0[i] = fmaf(qv.x, f0[0], acc0[i]); acc0[i] = fmaf(qv.y, f0[1], acc0[i]); acc0[i] = fmaf(qv.z, f0[2], acc0[i]); acc0[i] = fmaf(qv.w, f0[3], acc0[i]);
+            acc1[i] = fmaf(qv.x, f1[0], acc1[i]); acc1[i] = fmaf(qv.y, f1[1], acc1[i]); acc1[i] = fmaf(qv.z, f1[2], acc1[i]); acc1[i] = fmaf(qv.w, f1[3], acc1[i]);
+        }
+    }
     const float l2 = cum ? 0.f : log2f(decay[h]);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int t = t0 + tg * 8 + i;
-        if (t < len) {
-            float * o = out + (size_t) (start + t) * H * V + (size_t) h * V + v0 + vj;
-            *o = fmaf(cum ? cum[(size_t) (start + t) * ldc + h] : exp2f((float) (t + 1) * l2), acc[i], *o);
-        }
+        if (t >= len) continue;
+        const float c = cum ? cum[(size_t) (start + t) * ldc + h] : exp2f((float) (t + 1) * l2);
+        float * o = out + (size_t) (start + t) * H * V + (size_t) h * V + v0;
+        if (v0 + vj < V)      o[vj] = fmaf(c, acc0[i], o[vj]);
+        if (v0 + vj + 32 < V) o[vj + 32] = fmaf(c, acc1[i], o[vj + 32]);
     }
 }
 size_t pib_scan_split_bytes(int H, int D, int V, int parts) { return ((size_t) 2 * parts * H * D * V + 3 * (size_t) parts) * 4 + 64; }
@@ -656,7 +667,8 @@ static int scan_in_parts(int mode, ls_args A, const float * q, int ldq, const fl
     pib_launch(decay_split_combine_kernel, dim3((unsigned) ((E + 255) / 256)), dim3(256), (size_t) 0, st, (const float *) Lm, F, E, D * V, parts, (const int32_t *) table,
                decay, cum, ldc, b.seg_slot, state, state_stride, state_off);
     CKL();
-    const size_t smem = ((size_t) D * DF_VT + (size_t) DF_TT * D) * 4;
+    const size_t smem = (size_t) ((D + 3) & ~3) * (DF_VT + DF_TT) * 4;
+    if (smem > 200 * 1024) { pib_set_error("recurrence in parts: dim %d", D); return PIB_ERR_UNSUPP; }
     if (smem > 48 * 1024) cudaFuncSetAttribute(decay_split_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
     dim3 grid((unsigned) ((per + DF_TT - 1) / DF_TT), (unsigned) (H * ((V + DF_VT - 1) / DF_VT)), (unsigned) (parts - 1));
     pib_launch(decay_split_fixup_kernel, dim3(grid), dim3(256), (size_t) smem, st, q, ldq, (const float *) F, E, H, A.G, D, V, (const int32_t *) table, parts, decay, cum, ldc, A.out);
