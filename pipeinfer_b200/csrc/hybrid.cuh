@@ -152,9 +152,10 @@ struct pib_hybrid {
     float * loop_steps = nullptr;                     // [walks][width]
     int     n_cache = 0;
     std::vector<int> cache_row;                       // floats per cell of caching layer i
-    // YaRN scaling (factor > 0): with dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0),
-    // hi = min(ceil(dim(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency of pair i is
-    // f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1
+    // YaRN scaling (factor > 0).  d(n) = dims ln(original / (2 pi n)) / (2 ln base) is the pair index whose wave turns n times over the original
+    // context; pairs below a = max(floor(d(fast)), 0) keep their frequency, pairs above b = min(ceil(d(slow)), dims - 1) have it divided by
+    // the factor, and between them the blend r_i = clamp((i - a) / max(b - a, 0.001), 0, 1) gives f_i (r_i / factor + 1 - r_i).  The table's
+    // cos and sin carry the magnitude 0.1 ln(factor) + 1.
     struct Rope { float base; int dims; double factor = 0, original = 0, fast = 0, slow = 0; };
     std::vector<Rope> ropes;
     // widest per-token scratch rows over all layers

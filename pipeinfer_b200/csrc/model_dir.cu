@@ -828,7 +828,7 @@ static pib_model * build_putazen(const Json & cfg, TensorSource & src, int dtype
                     for (int64_t d = 0; d < D; d++) dots[i] += (double) a[(size_t) d] * (double) b[(size_t) d];
                 }
             }
-            L.diff_lambda = (float) (exp(dots[0]) - exp(dots[1]) + diff);       // one number for the layer
+            L.diff_lambda = (float) (exp(dots[0]) - exp(dots[1]) + diff);       // a scalar shared by every head of the layer
             L.diff_out = (float) (1.0 - diff);
             MAT(L.wo, px + "o", W, H * Vd);
             widen(hy->w_proj, (NQ + NK + NV + 3) & ~(int64_t) 3); widen(hy->w_q, NQ); widen(hy->w_lat, H * 2 * Vd); widen(hy->w_att, H * Vd);

@@ -44,7 +44,7 @@ def hyper_read(X, a):
 
 
 def hyper_write(X, M, b, y):
-    """all streams at once from the old ones: X'_t = sum_s M[s, t] X_s + b_t y"""
+    """X'_t = sum_s M[s, t] X_s + b_t y, every new stream formed from the streams as they were before the sublayer"""
     return np.einsum("su,Tsw->Tuw", M, X) + b[None, :, None] * y[:, None, :]
 
 
@@ -102,7 +102,7 @@ def mamba2(h, W, pre, mx, eps, st):
     if "S" not in st:
         st["S"] = np.zeros((H, N, P))
     y = scalar_decay_scan(x, dt, np.exp(W[pre + "A_log"]), B, C, W[pre + "D"], st["S"]).reshape(T, I)
-    y = grouped_rms(y * silu(z), mx["norm_groups"], W[pre + "norm"], eps)           # the gate comes before the norm
+    y = grouped_rms(y * silu(z), mx["norm_groups"], W[pre + "norm"], eps)           # gated first, normed after
     return y @ W[pre + "o"].T
 
 
