@@ -10,6 +10,8 @@
 //   PolyNorm, mixture-of-experts routing (softmax, top-k, renormalise), grouping of (token, expert) pairs by expert
 #include "hybrid.cuh"
 
+#include <algorithm>
+
 #include <cuda_bf16.h>
 
 #define CKL() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) { pib_set_error("%s:%d: launch failed: %s", __FILE__, __LINE__, cudaGetErrorString(e__)); return PIB_ERR_CUDA; } } while (0)
@@ -92,7 +94,7 @@ __global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x
     const int t = blockIdx.x, sg = seg[t], s0 = seg_start[sg];
     float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
     const bool single = (flags & CONV_MOVE_TAIL) != 0;    // a batch of decoded tokens only: this block is the tail's only reader and moves it on itself
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += blockDim.x * gridDim.y) {       // channels are independent: a token's may be spread over several blocks
         float acc = (flags & CONV_ADD_INPUT) ? x[(size_t) t * ldu + c] : 0.f;
         if (bias) acc += bias[c];
         for (int j = 0; j < taps; j++) {
@@ -135,7 +137,9 @@ int pib_chan_conv(const float * u, int ldu, const float * w, int taps, const pib
     // T == S: every segment is one token; its block moves the tail on itself and no tail kernel follows.  (In a batch that also holds longer
     // segments the tail kernel handles every segment, so no block may have moved a tail before it.)
     const int flags = (add_input ? CONV_ADD_INPUT : 0) | (silu ? CONV_SILU : 0) | (b.T == b.S ? CONV_MOVE_TAIL : 0);
-    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, u, ldu, w, taps, b.seg, b.seg_start, b.seg_slot, state, state_stride, tail_off, C, out, ldo, flags, bias);
+    // few tokens (decode steps): a token's channels go to several blocks, so that more than a handful of SMs have loads in flight
+    const unsigned ny = b.T > 32 ? 1u : (unsigned) std::min(16, (C + 255) / 256);
+    pib_launch(canon_kernel, dim3((unsigned) b.T, ny), dim3(256), (size_t) (0), st, u, ldu, w, taps, b.seg, b.seg_start, b.seg_slot, state, state_stride, tail_off, C, out, ldo, flags, bias);
     CKL();
     if (taps > 1 && b.T > b.S) { pib_launch(canon_tail_kernel, dim3(b.S), dim3(256), (size_t) (0), st, u, ldu, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, C); CKL(); }
     return PIB_OK;

@@ -29,7 +29,7 @@ __device__ __forceinline__ float sk_silu(float z) { return z / (1.0f + expf(-z))
 // written; hc_in: the read weights of the sublayer that follows (null: every stream counts once, the model's output); h [T][W] receives
 // LayerNorm(u) * w + bias (null: only the write is done).  One block per token; a thread owns its columns in all streams.
 template <int MAXS>
-__global__ void __launch_bounds__(256) hyper_norm_kernel(float * __restrict__ X, int S, const float * __restrict__ y, const float * __restrict__ hc_prev,
+__global__ void __launch_bounds__(MAXS <= 4 ? 1024 : 256) hyper_norm_kernel(float * __restrict__ X, int S, const float * __restrict__ y, const float * __restrict__ hc_prev,
                                                          const float * __restrict__ hc_in, const float * __restrict__ w, const float * __restrict__ bias, float eps, int W,
                                                          float * __restrict__ h) {
     pib_pdl_wait();
@@ -84,7 +84,9 @@ __global__ void __launch_bounds__(256) hyper_norm_kernel(float * __restrict__ X,
 int pib_hyper_norm(float * X, int S, const float * y, const float * hc_prev, const float * hc_in, const float * w, const float * bias, float eps, int T, int W, float * h,
                    cudaStream_t st) {
     if (S < 1 || S > 16) { pib_set_error("hyper-connections: %d streams (1 to 16)", S); return PIB_ERR_UNSUPP; }
-    if (S <= 4) pib_launch(hyper_norm_kernel<4>, dim3(T), dim3(256), (size_t) W * 4, st, X, S, y, hc_prev, hc_in, w, bias, eps, W, h);
+    // a decode step has one CTA per sequence: more threads keep more of the row's loads in flight (prompts fill the GPU with 256-thread CTAs)
+    const int threads = T > 32 ? 256 : W >= 2048 ? 1024 : W >= 1024 ? 512 : 256;
+    if (S <= 4) pib_launch(hyper_norm_kernel<4>, dim3(T), dim3(threads), (size_t) W * 4, st, X, S, y, hc_prev, hc_in, w, bias, eps, W, h);
     else        pib_launch(hyper_norm_kernel<16>, dim3(T), dim3(256), (size_t) W * 4, st, X, S, y, hc_prev, hc_in, w, bias, eps, W, h);
     CKL();
     return PIB_OK;
@@ -140,7 +142,7 @@ int pib_mamba2_prep(const float * proj, int ldp, int dt_off, const pib_hlayer & 
 }
 
 // y [T][C] <- (y silu(z)) / sqrt(mean over the part + eps) * w, the C channels in `groups` equal parts; z rows have pitch ldz.  Grid (token, part).
-__global__ void __launch_bounds__(256) gated_group_norm_kernel(float * __restrict__ y, const float * __restrict__ z, int ldz, int C, int gs, const float * __restrict__ w, float eps) {
+__global__ void __launch_bounds__(1024) gated_group_norm_kernel(float * __restrict__ y, const float * __restrict__ z, int ldz, int C, int gs, const float * __restrict__ w, float eps) {
     pib_pdl_wait();
     pib_pdl_trigger();
     __shared__ float red[32];
@@ -154,7 +156,8 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(float * __restric
 }
 int pib_gated_group_norm(float * y, const float * z, int ldz, int T, int C, int groups, const float * w, float eps, cudaStream_t st) {
     if (groups < 1 || C % groups) { pib_set_error("grouped norm: %d channels in %d parts", C, groups); return PIB_ERR_ARG; }
-    pib_launch(gated_group_norm_kernel, dim3((unsigned) T, (unsigned) groups), dim3(256), (size_t) 0, st, y, z, ldz, C, C / groups, w, eps);
+    const int gs = C / groups, threads = T > 32 ? 256 : gs >= 2048 ? 1024 : gs >= 1024 ? 512 : 256;     // decode steps: more of a part's loads in flight
+    pib_launch(gated_group_norm_kernel, dim3((unsigned) T, (unsigned) groups), dim3(threads), (size_t) 0, st, y, z, ldz, C, gs, w, eps);
     CKL();
     return PIB_OK;
 }
@@ -162,7 +165,7 @@ int pib_gated_group_norm(float * y, const float * z, int ldz, int T, int C, int 
 // ---- attention with several maps per head ---------------------------------------------------------------------------------------------------
 // proj[t] = [q (H * maps * D) | k (G * maps * D) | v (G * V)]; bias over all rows (null: none).  Within every D-wide chunk of q and k the
 // first rot_dims coordinates turn by the token's angles.  q[t] gets the query rows, the token's cell [k | v].
-__global__ void __launch_bounds__(256) qkv_rope_kernel(const float * __restrict__ proj, int ldp, int nq, int nk, int nv, int D, int rot_dims, int pairs, const float * __restrict__ bias,
+__global__ void __launch_bounds__(1024) qkv_rope_kernel(const float * __restrict__ proj, int ldp, int nq, int nk, int nv, int D, int rot_dims, int pairs, const float * __restrict__ bias,
                                                        const int32_t * __restrict__ pos, const int32_t * __restrict__ cell, const float2 * __restrict__ rope,
                                                        float * __restrict__ q, float * __restrict__ cache, int cache_row) {
     pib_pdl_wait();
@@ -188,7 +191,8 @@ __global__ void __launch_bounds__(256) qkv_rope_kernel(const float * __restrict_
     }
 }
 int pib_qkv_rope(const float * proj, int ldp, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, float * q, float * cache, int cache_row, cudaStream_t st) {
-    pib_launch(qkv_rope_kernel, dim3(b.T), dim3(256), (size_t) 0, st, proj, ldp, L.heads * L.maps * L.dim, L.kv_heads * L.maps * L.dim, L.kv_heads * L.vdim, L.dim, L.rot_dims,
+    const int n_all = (L.heads + L.kv_heads) * L.maps * L.dim + L.kv_heads * L.vdim, threads = b.T > 32 ? 256 : n_all >= 2048 ? 1024 : n_all >= 1024 ? 512 : 256;
+    pib_launch(qkv_rope_kernel, dim3(b.T), dim3(threads), (size_t) 0, st, proj, ldp, L.heads * L.maps * L.dim, L.kv_heads * L.maps * L.dim, L.kv_heads * L.vdim, L.dim, L.rot_dims,
                L.rot_pairs, (const float *) L.proj_bias, b.pos, b.cell, rope, q, cache, cache_row);
     CKL();
     return PIB_OK;
