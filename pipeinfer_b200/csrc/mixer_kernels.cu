@@ -379,6 +379,7 @@ struct ls_args {
     const int32_t * seg_start, * seg_len, * seg_slot;
     float * state; size_t state_stride, state_off;
     float * out;                             // [T][H][V]
+    int vec16;                               // set by lin_scan: the operand rows start on 16-byte boundaries and D is a multiple of 4 (staged in 16-byte pieces)
 };
 __device__ __forceinline__ float ls_sum16(float x) {
     x += __shfl_xor_sync(0xffffffffu, x, 1);
@@ -395,7 +396,7 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
     const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LS_VT, part = threadIdx.x & 15, vl = threadIdx.x >> 4, vd = v0 + vl;
     const int D = FULL ? 16 * RPT : A.D, V = A.V, H = A.H, grp = h / (H / A.G), CH = A.chunk;
     const int s0 = A.seg_start[sg], n = A.seg_len[sg];
-    const int vbase = MODE == 0 ? 3 * D : 2 * D, dot_off = vbase + LS_VT + ((MODE == 1 || MODE == 3) ? 2 : 0), row_f = dot_off + 1;
+    const int vbase = MODE == 0 ? 3 * D : 2 * D, dot_off = vbase + LS_VT + ((MODE == 1 || MODE == 3) ? 2 : 0), row_f = (dot_off + 4) & ~3;
     const float cdec = MODE == 2 ? A.w[h] : 0.f, skip = MODE == 3 ? A.u[h] : 0.f;
     const bool vok = vd < V;
     float * S = A.state + (size_t) A.seg_slot[sg] * A.state_stride + A.state_off + (size_t) h * D * V;
@@ -408,6 +409,31 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
     }
     auto fetch = [&](int c0, int buf) {
         const int nc = min(CH, n - c0);
+        if (A.vec16) {
+            // the chunk's operand rows as one list of 16-byte pieces (token, operand, piece) spread over the threads, then the tokens' few
+            // scalars the same way: a thread forms an address per copy, not per token
+            const uint32_t base = (uint32_t) __cvta_generic_to_shared(hs + (size_t) buf * CH * row_f);
+            const int nv = D >> 2, NP = (MODE == 0 ? 3 : 2) * nv;
+            for (int p = threadIdx.x; p < nc * NP; p += blockDim.x) {
+                const int t = p / NP, e = p - t * NP, which = e / nv, i = e - which * nv;
+                const size_t tt = (size_t) (s0 + c0 + t);
+                const float * src = which == 0 ? A.a + tt * A.lda + (size_t) grp * A.a_hs : which == 1 ? A.k + tt * A.ldk + (size_t) grp * A.k_hs : A.w + tt * A.ldw + (size_t) h * D;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + 4u * (uint32_t) (t * row_f + which * D + 4 * i)), "l"(src + 4 * i) : "memory");
+            }
+            constexpr int NS = LS_VT + ((MODE == 1 || MODE == 3) ? 2 : 0);
+            for (int p = threadIdx.x; p < nc * NS; p += blockDim.x) {
+                const int t = p / NS, j = p - t * NS;
+                const size_t tt = (size_t) (s0 + c0 + t);
+                const uint32_t dst = base + 4u * (uint32_t) (t * row_f + vbase + j);
+                if (j < LS_VT) {
+                    if (v0 + j < V) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(A.v + tt * A.ldv + (size_t) h * V + v0 + j) : "memory");
+                } else {
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(A.w + tt * A.ldw + (j == LS_VT ? H : 0) + h) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
         for (int t = 0; t < nc; t++) {
             const size_t tt = (size_t) (s0 + c0 + t);
             const float * ar = A.a + tt * A.lda + (size_t) grp * A.a_hs;
@@ -525,7 +551,13 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
 static int lin_scan(int mode, ls_args & A, int S, cudaStream_t st) {
     if (A.D > 256) { pib_set_error("recurrence: dim %d not supported (up to 256)", A.D); return PIB_ERR_UNSUPP; }
     dim3 grid((unsigned) S, (unsigned) A.H, (unsigned) ((A.V + LS_VT - 1) / LS_VT));
-    const size_t row_f = (size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + ((mode == 1 || mode == 3) ? 2 : 0) + 1;
+    const size_t row_f = ((size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + ((mode == 1 || mode == 3) ? 2 : 0) + 4) & ~(size_t) 3;
+    {   // 16-byte staging copies need every operand row to start on a 16-byte boundary
+        static const int on = getenv("PIB_SCAN_VEC") ? atoi(getenv("PIB_SCAN_VEC")) : 1;
+        auto al = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
+        A.vec16 = on && A.D % 4 == 0 && al(A.a) && al(A.k) && A.lda % 4 == 0 && A.ldk % 4 == 0 && A.a_hs % 4 == 0 && A.k_hs % 4 == 0 &&
+                  (mode != 0 || (al(A.w) && A.ldw % 4 == 0));
+    }
     // chunks of 32 tokens halve the barriers per token, but their double buffer must not push part of the grid into a second wave
     const size_t smem32 = row_f * 4 * 2 * 32;
     const size_t per_sm = smem32 <= 100 * 1024 ? (size_t) (227 * 1024) / (smem32 + 1024) : 0;
